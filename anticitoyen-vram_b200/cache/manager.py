@@ -77,6 +77,9 @@ class PagedNeed:
     value_dim: int = 0      # elements of a value row; 0: as many as a key row
     chunk: int = 0
     keep_first: int = 0     # with a window: the first tokens of a request that every later token may still read
+    # the values are the first ``value_dim`` elements of the key rows themselves (one kept row per token that is read
+    # as key and as value): the group then has no value pages
+    value_in_key: bool = False
 
     @property
     def kind(self) -> str:
@@ -108,11 +111,12 @@ class PagedNeed:
     def widened(self, other: "PagedNeed") -> "PagedNeed":
         """The need of a cache slot that mixers with this need and with ``other`` both read: rows of the same
         sizes, and whatever either of them may read again is kept (different rules of forgetting: everything)."""
-        if (self.num_kv_heads, self.head_dim, self.value_size) != (other.num_kv_heads, other.head_dim, other.value_size):
+        if (self.num_kv_heads, self.head_dim, self.value_size, self.value_in_key) != \
+                (other.num_kv_heads, other.head_dim, other.value_size, other.value_in_key):
             raise ValueError(f"{self} and {other} cannot share a cache slot: their rows differ")
         if (self.window, self.chunk, self.keep_first) == (other.window, other.chunk, other.keep_first):
             return self
-        return PagedNeed(self.num_kv_heads, self.head_dim, 0, self.value_dim, 0)
+        return PagedNeed(self.num_kv_heads, self.head_dim, 0, self.value_dim, 0, 0, self.value_in_key)
 
 
 @dataclass(frozen=True)

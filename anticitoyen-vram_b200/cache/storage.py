@@ -14,7 +14,9 @@ class CacheStorage:
     index 0 of the second axis, values at 1); a page of one kv-head is contiguous,
     so a tile of keys is a run of ``page_size * head_dim`` elements.  Where a value
     row has another size than a key row, keys and values are two tensors,
-    ``[slots, num_pages, kv_heads, page_size, head_dim]`` and ``[..., value_dim]``.  The
+    ``[slots, num_pages, kv_heads, page_size, head_dim]`` and ``[..., value_dim]``; where
+    the values are part of the key rows (``PagedNeed.value_in_key``) there is the key
+    tensor alone, handed out as both.  The
     reference keeps ``[num_blocks, 16, kv_heads, head_dim]`` per layer
     (acvram/memory/kvcache.py:463-469).  State group:
     ``[slots, max_requests + 1, *shape]`` (the last slot belongs to nobody: padding rows of a
@@ -32,10 +34,16 @@ class CacheStorage:
         self.tensors: list[torch.Tensor] = []
         self.value_tensors: dict[int, torch.Tensor] = {}    # group index -> values, where their rows differ from the keys'
         self.tables: dict[int, torch.Tensor] = {}       # group index -> the group's block table on the device
+        self.keys_only: set[int] = set()                # groups whose values live inside their key rows
         for gi, g in enumerate(manager.groups):
             if isinstance(g, PagedGroup):
                 pages = max(g.pool.num_pages, 1)
-                if g.need.value_size == g.need.head_dim:
+                if getattr(g.need, "value_in_key", False):
+                    # one kept row per token serves as key and as value: keys only
+                    shape = (g.num_slots, pages, g.need.num_kv_heads, g.page_size, g.need.head_dim)
+                    self.tensors.append(torch.zeros(shape, device=self.device, dtype=dtype))
+                    self.keys_only.add(gi)
+                elif g.need.value_size == g.need.head_dim:
                     shape = (g.num_slots, 2, pages, g.need.num_kv_heads, g.page_size, g.need.head_dim)
                     self.tensors.append(torch.zeros(shape, device=self.device, dtype=dtype))
                 else:
@@ -67,6 +75,8 @@ class CacheStorage:
         g, i = plan.group_of_slot[cache_slot], plan.index_in_group[cache_slot]
         if g in self.value_tensors:
             return self.tensors[g][i], self.value_tensors[g][i]
+        if g in self.keys_only:
+            return self.tensors[g][i], self.tensors[g][i]
         t = self.tensors[g][i]
         return t[0], t[1]
 

@@ -1,5 +1,7 @@
 // Paged causal attention, generic form: any number of query tokens per request,
-// any head size up to 256 (value rows may have another size than key rows, DV != D), float or bfloat16 pages.  One warp per
+// any head size up to 1024 (value rows may have another size than key rows, DV != D, up to 512; with v_pages == k_pages
+// and v_row = D the values are the first DV elements of the key rows themselves: one kept row per token serves as key
+// and as value, as a latent that every head reads does), float or bfloat16 pages.  One warp per
 // (query token, query head).  It is the 32-bit path of the engine and the
 // fallback of the bfloat16 path for head sizes the tensor-core kernels do not take.
 //
@@ -20,7 +22,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
                                     const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ bt_rows, int NH, int NKV, int D, int DV,
-                                    int page_size, int num_pages, float scale, int window, int keep_first) {
+                                    int page_size, int num_pages, float scale, int window, int keep_first, int v_row) {
     extern __shared__ float sm_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y * AG_WARPS + warp;
@@ -58,7 +60,20 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
         if (valid) {
             const T* kr = k_pages + row * D;
             float dot = 0.f;
-            for (int e = 0; e < D; ++e) dot = fmaf(qs[e], to_f32(kr[e]), dot);
+            if ((D & 7) == 0 && sizeof(T) == 2) {       // rows of 16-byte pieces: eight elements a load
+                const uint4* kv = reinterpret_cast<const uint4*>(kr);
+                for (int e = 0; e < D; e += 8) {
+                    const uint4 u = kv[e >> 3];
+                    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        dot = fmaf(qs[e + 2 * i], __uint_as_float(w4[i] << 16), dot);
+                        dot = fmaf(qs[e + 2 * i + 1], __uint_as_float(w4[i] & 0xffff0000u), dot);
+                    }
+                }
+            } else {
+                for (int e = 0; e < D; ++e) dot = fmaf(qs[e], to_f32(kr[e]), dot);
+            }
             s = dot;
         }
         const float tmax = warp_max(s);
@@ -75,7 +90,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
             const float pk = __shfl_sync(0xffffffffu, pl, kk);
             const long long ro = __shfl_sync(0xffffffffu, row, kk);
             if (pk == 0.f) continue;
-            const T* vr = v_pages + ro * DV;
+            const T* vr = v_pages + ro * v_row;
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
                 const int e = lane + 32 * r;
@@ -97,7 +112,7 @@ template <typename T>
 static int launch_generic(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                           const void* v_pages, const int* positions, const int* seq_of_token, const int* block_table,
                           int bt_stride, const int* bt_rows, int T_tokens, int NH, int NKV, int D, int DV, int page_size, int num_pages,
-                          float scale, int window, int keep_first, cudaStream_t stream) {
+                          float scale, int window, int keep_first, int v_row, cudaStream_t stream) {
     dim3 grid(T_tokens, (NH + AG_WARPS - 1) / AG_WARPS);
     const size_t smem = (size_t)AG_WARPS * D * sizeof(float);
     const int nr = (DV + 31) / 32;
@@ -105,10 +120,11 @@ static int launch_generic(const void* q, int q_stride, void* out, int out_stride
     case N:                                                                                                          \
         attn_generic_kernel<T, N><<<grid, AG_WARPS * 32, smem, stream>>>(                                            \
             (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, positions,             \
-            seq_of_token, block_table, bt_stride, bt_rows, NH, NKV, D, DV, page_size, num_pages, scale, window, keep_first);                \
+            seq_of_token, block_table, bt_stride, bt_rows, NH, NKV, D, DV, page_size, num_pages, scale, window, keep_first, v_row);                \
         break;
     switch (nr) {
         AG_CASE(1) AG_CASE(2) AG_CASE(3) AG_CASE(4) AG_CASE(5) AG_CASE(6) AG_CASE(7) AG_CASE(8)
+        AG_CASE(9) AG_CASE(10) AG_CASE(11) AG_CASE(12) AG_CASE(13) AG_CASE(14) AG_CASE(15) AG_CASE(16)
         default: return ACV_ERR_SIZE;
     }
 #undef AG_CASE
@@ -122,14 +138,17 @@ ACV_API int acv_attention_generic(const void* q, int q_stride, void* out, int ou
                                   int value_dim, int keep_first, cudaStream_t stream) {
     if (T_tokens <= 0) return 0;
     const int DV = value_dim > 0 ? value_dim : D;
-    if (D <= 0 || D > 256 || DV > 256 || NKV <= 0 || NH % NKV) return ACV_ERR_SIZE;
+    if (D <= 0 || D > 1024 || DV > 512 || NKV <= 0 || NH % NKV) return ACV_ERR_SIZE;
+    // values inside the key rows: the same pages, rows of D elements
+    const int v_row = v_pages == k_pages ? D : DV;
+    if (v_row < DV) return ACV_ERR_SIZE;
     if (dtype == ACV_F32)
         return launch_generic<float>(q, q_stride, out, out_stride, k_pages, v_pages, positions, seq_of_token,
                                      block_table, bt_stride, bt_rows, T_tokens, NH, NKV, D, DV, page_size, num_pages, scale, window,
-                                     keep_first, stream);
+                                     keep_first, v_row, stream);
     if (dtype == ACV_BF16)
         return launch_generic<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, positions, seq_of_token,
                                     block_table, bt_stride, bt_rows, T_tokens, NH, NKV, D, DV, page_size, num_pages, scale, window,
-                                    keep_first, stream);
+                                    keep_first, v_row, stream);
     return ACV_ERR_DTYPE;
 }

@@ -16,7 +16,11 @@
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TI* __restrict__ A, int lda, const TI* __restrict__ W, int ldw, TO* __restrict__ C, int ldc,
-                 int M, int N, int K) {
+                 int M, int N, int K, long long a_batch, long long w_batch, long long c_batch) {
+    // blockIdx.z: one product of a batch (A, W and C each move by their batch stride, in elements)
+    A += (size_t)blockIdx.z * a_batch;
+    W += (size_t)blockIdx.z * w_batch;
+    C += (size_t)blockIdx.z * c_batch;
     __shared__ float As[GS_BK][GS_BM + 4];
     __shared__ float Ws[GS_BK][GS_BN + 4];
     const int tid = threadIdx.x;
@@ -64,20 +68,27 @@ gemm_simt_kernel(const TI* __restrict__ A, int lda, const TI* __restrict__ W, in
     }
 }
 
-// in_dtype: type of A and W; out_dtype: type of C.
-ACV_API int acv_gemm_simt(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
-                          int in_dtype, int out_dtype, cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return 0;
+// in_dtype: type of A and W; out_dtype: type of C.  `batches` products side by side (a head's own matrix for each
+// head, say): product b reads A + b a_batch, W + b w_batch and writes C + b c_batch (strides in elements).
+ACV_API int acv_gemm_simt_batched(const void* A, int lda, long long a_batch, const void* W, int ldw, long long w_batch,
+                                  void* C, int ldc, long long c_batch, int M, int N, int K, int batches, int in_dtype,
+                                  int out_dtype, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batches <= 0) return 0;
     if (K <= 0) return ACV_ERR_SIZE;
-    dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM);
-    if (grid.y > 65535) return ACV_ERR_SIZE;
+    dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM, batches);
+    if (grid.y > 65535 || batches > 65535) return ACV_ERR_SIZE;
     if (in_dtype == ACV_F32 && out_dtype == ACV_F32)
-        gemm_simt_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)A, lda, (const float*)W, ldw, (float*)C, ldc, M, N, K);
+        gemm_simt_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)A, lda, (const float*)W, ldw, (float*)C, ldc, M, N, K, a_batch, w_batch, c_batch);
     else if (in_dtype == ACV_BF16 && out_dtype == ACV_F32)
-        gemm_simt_kernel<bf16, float><<<grid, 256, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, ldw, (float*)C, ldc, M, N, K);
+        gemm_simt_kernel<bf16, float><<<grid, 256, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, ldw, (float*)C, ldc, M, N, K, a_batch, w_batch, c_batch);
     else if (in_dtype == ACV_BF16 && out_dtype == ACV_BF16)
-        gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, ldw, (bf16*)C, ldc, M, N, K);
+        gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)A, lda, (const bf16*)W, ldw, (bf16*)C, ldc, M, N, K, a_batch, w_batch, c_batch);
     else
         return ACV_ERR_DTYPE;
     return acv_launch_status();
+}
+
+ACV_API int acv_gemm_simt(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
+                          int in_dtype, int out_dtype, cudaStream_t stream) {
+    return acv_gemm_simt_batched(A, lda, 0, W, ldw, 0, C, ldc, 0, M, N, K, 1, in_dtype, out_dtype, stream);
 }

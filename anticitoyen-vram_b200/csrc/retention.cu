@@ -4,7 +4,7 @@
 //   o_t = S_t^T q_t
 //
 // q and k are rotated by position (rotate-half over the first `rot` elements, cos and sin from a table) and k is
-// multiplied by k_scale, all in float, as they are staged; scores, state and sums are 32-bit.  A second kernel
+// multiplied by k_scale, all in float, as they are staged (with `act` set, q, k and v first pass through silu); scores, state and sums are 32-bit.  A second kernel
 // brings each head's o to unit RMS (no weight), multiplies by silu(gate) and a constant, and rounds once.
 //
 // acv_retention: grid (items, heads, tiles of DVT value columns: the columns of S do not know of one another, and a
@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
                                  const int* __restrict__ positions, const float* __restrict__ decay, float k_scale,
                                  float* __restrict__ state, const int* __restrict__ slots,
                                  const int* __restrict__ cu_q, RetSegments sg, float* __restrict__ o, int ldo, int H, int D, int DV,
-                                 int G, int TC, int DVT) {
+                                 int G, int TC, int DVT, int act) {
     extern __shared__ float sm[];
     float* qs = sm;                         // [TC][D]
     float* ks = qs + (size_t)TC * D;        // [TC][D]
@@ -89,12 +89,19 @@ __global__ void __launch_bounds__(ret_max_threads(R)) retention_kernel(const T* 
         for (int i = tid; i < n * D; i += nthr) {
             const int tt = i / D, e = i - tt * D;
             const size_t at = (size_t)(tb + tt) * ld + (size_t)h * D + e;
-            qs[i] = to_f32(q[at]);
-            ks[i] = to_f32(k[at]) * k_scale;
+            float qv = to_f32(q[at]), kv = to_f32(k[at]);
+            if (act) {          // silu of the projections, in float, before anything else
+                qv = qv / (1.f + expf(-qv));
+                kv = kv / (1.f + expf(-kv));
+            }
+            qs[i] = qv;
+            ks[i] = kv * k_scale;
         }
         for (int i = tid; i < n * DVT; i += nthr) {
             const int tt = i / DVT, e = i - tt * DVT;
-            vs[i] = c0 + e < DV ? to_f32(v[(size_t)(tb + tt) * ld + (size_t)h * DV + c0 + e]) : 0.f;
+            float vv = c0 + e < DV ? to_f32(v[(size_t)(tb + tt) * ld + (size_t)h * DV + c0 + e]) : 0.f;
+            if (act) vv = vv / (1.f + expf(-vv));
+            vs[i] = vv;
         }
         __syncthreads();
         if (cos_sin) {
@@ -190,7 +197,7 @@ template <typename T, int R>
 static int launch_retention(const void* q, const void* k, const void* v, int ld, const float* cos_sin, int rot,
                             int table_rows, const int* positions, const float* decay, float k_scale, float* state,
                             const int* slots, const int* cu_q, RetSegments sg, int summaries, float* o, int ldo, int num_seqs, int H, int D, int DV,
-                            int DVT, cudaStream_t stream) {
+                            int DVT, int act, cudaStream_t stream) {
     const int G = (D + R - 1) / R;
     const int threads = ((G * DVT + 31) / 32) * 32;
     const size_t per_token = (size_t)(2 * D + DVT + G * DVT) * sizeof(float);
@@ -208,11 +215,11 @@ static int launch_retention(const void* q, const void* k, const void* v, int ld,
     }
     if (summaries) {
         acv_launch(PDL_ATTN, retention_kernel<T, R, true>, grid, threads, smem, stream, (const T*)q, (const T*)k,
-                   (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC, DVT);
+                   (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC, DVT, act);
         acv_launch(PDL_ATTN, retention_fold_kernel, dim3(num_seqs, H, (D * DV + 255) / 256), 256, 0, stream, sg, cu_q, decay, H, D * DV);
     }
     acv_launch(PDL_ATTN, retention_kernel<T, R, false>, grid, threads, smem, stream, (const T*)q, (const T*)k,
-               (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC, DVT);
+               (const T*)v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC, DVT, act);
     return acv_launch_status();
 }
 
@@ -220,11 +227,11 @@ template <typename T>
 static int retention_by_rows(int R, const void* q, const void* k, const void* v, int ld, const float* cos_sin, int rot,
                              int table_rows, const int* positions, const float* decay, float k_scale, float* state,
                              const int* slots, const int* cu_q, RetSegments sg, int summaries, float* o, int ldo, int num_seqs, int H, int D, int DV,
-                             int DVT, cudaStream_t stream) {
+                             int DVT, int act, cudaStream_t stream) {
 #define RET_CASE(N)                                                                                                  \
     case N:                                                                                                          \
         return launch_retention<T, N>(q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots, \
-                                      cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, DVT, stream);
+                                      cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, DVT, act, stream);
     switch (R) {
         RET_CASE(4) RET_CASE(8) RET_CASE(16) RET_CASE(32) RET_CASE(64)
     }
@@ -240,7 +247,7 @@ ACV_API int acv_retention(const void* q, const void* k, const void* v, int ld, c
                           int table_rows, const int* positions, const float* decay, float k_scale, float* state,
                           const int* slots, const int* cu_q, const int* seg_seq, const int* seg_idx, int seg_len,
                           float* seg_state, int summaries, float* o, int ldo, int n_items, int H, int D, int DV,
-                          int dtype, cudaStream_t stream) {
+                          int dtype, int act, cudaStream_t stream) {
     const int num_seqs = n_items;
     if (num_seqs <= 0) return 0;
     if (H <= 0 || D <= 0 || DV <= 0 || (cos_sin && (rot <= 0 || rot > D || (rot & 1)))) return ACV_ERR_SIZE;
@@ -270,48 +277,57 @@ ACV_API int acv_retention(const void* q, const void* k, const void* v, int ld, c
     if (!R) return ACV_ERR_SIZE;          // (key rows of more than 512 elements are not built)
     if (dtype == ACV_F32)
         return retention_by_rows<float>(R, q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots,
-                                        cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, DVT, stream);
+                                        cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, DVT, act, stream);
     if (dtype == ACV_BF16)
         return retention_by_rows<bf16>(R, q, k, v, ld, cos_sin, rot, table_rows, positions, decay, k_scale, state, slots,
-                                       cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, DVT, stream);
+                                       cu_q, sg, summaries, o, ldo, num_seqs, H, D, DV, DVT, act, stream);
     return ACV_ERR_DTYPE;
 }
 
-// ----------------------------------------------------------------------------- unit RMS per head, gate, constant
-// out[t][h*DV + e] = o / sqrt(mean_e(o^2) + eps) * silu(gate) * out_scale; one warp per (token, head).
+// ----------------------------------------------------------------------------- unit RMS, weight, gate, constant
+// out[t][u*group + e] = o / sqrt(mean_e(o^2) + eps) * w[u*group + e] * gate_fn(gate) * out_scale over groups of `group`
+// elements (a head's DV: each head by itself; all H*DV: the heads side by side normed together); w null: no weight;
+// gate_fn silu (0) or sigmoid (1).  One warp per (token, group).
 template <typename T>
 __global__ void retention_gate_kernel(const float* __restrict__ o, int ldo, const T* __restrict__ gate, int ldg,
-                                      T* __restrict__ out, int ld_out, int H, int DV, float eps, float out_scale, int T_tokens) {
+                                      T* __restrict__ out, int ld_out, int groups, int group, const float* __restrict__ w,
+                                      int gate_kind, float eps, float out_scale, int T_tokens) {
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int unit = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (unit >= T_tokens * H) return;
-    const int t = unit / H, h = unit - t * H;
-    const float* orow = o + (size_t)t * ldo + (size_t)h * DV;
+    if (unit >= T_tokens * groups) return;
+    const int t = unit / groups, u = unit - t * groups;
+    const float* orow = o + (size_t)t * ldo + (size_t)u * group;
     float ss = 0.f;
-    for (int e = lane; e < DV; e += 32) ss = fmaf(orow[e], orow[e], ss);
+    for (int e = lane; e < group; e += 32) ss = fmaf(orow[e], orow[e], ss);
     ss = warp_sum(ss);
-    const float inv = out_scale / sqrtf(ss / (float)DV + eps);
-    const T* grow = gate + (size_t)t * ldg + (size_t)h * DV;
-    T* dst = out + (size_t)t * ld_out + (size_t)h * DV;
-    for (int e = lane; e < DV; e += 32) {
+    const float inv = out_scale / sqrtf(ss / (float)group + eps);
+    const T* grow = gate + (size_t)t * ldg + (size_t)u * group;
+    const float* wr = w ? w + (size_t)u * group : nullptr;
+    T* dst = out + (size_t)t * ld_out + (size_t)u * group;
+    for (int e = lane; e < group; e += 32) {
         const float z = to_f32(grow[e]);
-        dst[e] = from_f32<T>(orow[e] * inv * (z / (1.f + expf(-z))));
+        const float sg = 1.f / (1.f + expf(-z));
+        float v = orow[e] * inv;
+        if (wr) v *= wr[e];
+        dst[e] = from_f32<T>(v * (gate_kind == 1 ? sg : z * sg));
     }
 }
 
 ACV_API int acv_retention_gate(const float* o, int ldo, const void* gate, int ldg, void* out, int ld_out, int T_tokens,
-                               int H, int DV, float eps, float out_scale, int dtype, cudaStream_t stream) {
+                               int H, int DV, float eps, float out_scale, int dtype, const float* weight, int joint,
+                               int gate_kind, cudaStream_t stream) {
     if (T_tokens <= 0) return 0;
     const int warps = 8;
-    const int grid = (T_tokens * H + warps - 1) / warps;
+    const int groups = joint ? 1 : H, group = joint ? H * DV : DV;
+    const int grid = (T_tokens * groups + warps - 1) / warps;
     if (dtype == ACV_F32)
         acv_launch(PDL_MISC, retention_gate_kernel<float>, grid, warps * 32, 0, stream, o, ldo, (const float*)gate, ldg,
-                   (float*)out, ld_out, H, DV, eps, out_scale, T_tokens);
+                   (float*)out, ld_out, groups, group, weight, gate_kind, eps, out_scale, T_tokens);
     else if (dtype == ACV_BF16)
         acv_launch(PDL_MISC, retention_gate_kernel<bf16>, grid, warps * 32, 0, stream, o, ldo, (const bf16*)gate, ldg,
-                   (bf16*)out, ld_out, H, DV, eps, out_scale, T_tokens);
+                   (bf16*)out, ld_out, groups, group, weight, gate_kind, eps, out_scale, T_tokens);
     else
         return ACV_ERR_DTYPE;
     return acv_launch_status();

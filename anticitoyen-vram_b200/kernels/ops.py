@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import math
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -80,9 +81,16 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_block_gates": [P, P, P, P, P, P, F, P, P, I, I, I, P],
         "acv_block_gates_mma": [P, P, P, P, P, P, F, P, P, I, I, I, P],
         "acv_gated_scan": [P, P, P, I, P, P, P, P, P, P, I, P, I, P, I, I, I, I, I, P],
-        "acv_retention": [P, P, P, I, P, I, I, P, P, F, P, P, P, P, P, I, P, I, P, I, I, I, I, I, I, P],
-        "acv_retention_gate": [P, I, P, I, P, I, I, I, I, F, F, I, P],
+        "acv_retention": [P, P, P, I, P, I, I, P, P, F, P, P, P, P, P, I, P, I, P, I, I, I, I, I, I, I, P],
+        "acv_retention_gate": [P, I, P, I, P, I, I, I, I, F, F, I, P, I, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
+        "acv_gemm_simt_batched": [P, I, LL, P, I, LL, P, I, LL, I, I, I, I, I, I, P],
+        "acv_attention_mixed": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P, F, P, P, I, I, P, I, P],
+        "acv_add_normed_rmsnorm": [P, P, I, P, F, P, F, P, I, I, I, P],
+        "acv_cast_rows_f32": [P, I, P, I, I, I, I, P],
+        "acv_activation": [P, P, LL, I, F, F, I, P],
+        "acv_rmsnorm_rows": [P, I, P, F, P, I, I, I, I, P],
+        "acv_latent_prepare": [P, I, P, I, P, I, P, F, P, I, I, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P],
         "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, P, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
         "acv_gemm_tc_bias": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P, P],
@@ -1404,11 +1412,12 @@ def gated_scan(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, y_bias: torch.
 def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_sin: torch.Tensor | None, positions: torch.Tensor,
               decay: torch.Tensor, k_scale: float, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor,
               num_seqs: int, out: torch.Tensor, num_heads: int, dim: int, value_dim: int,
-              work: dict | None = None) -> torch.Tensor:
+              work: dict | None = None, silu_inputs: bool = False) -> torch.Tensor:
     """S = decay_h S + k v^T, o = S^T q along each request's tokens, per head; q, k ([T, H*dim]) and v ([T, H*value_dim])
     are views of one projection (same row stride); q and k are rotated by ``cos_sin`` (float32 [positions, rot]) and k
     multiplied by ``k_scale`` in float; state float32 [slots, H, dim, value_dim]; out float32 [T, H*value_dim].
-    ``work``: the step's segments (``segment_work``); default: every request's portion is one item."""
+    ``work``: the step's segments (``segment_work``); default: every request's portion is one item.
+    ``silu_inputs``: q, k and v pass through silu, in float, before anything else."""
     _need_cuda(q, k, v, state, out)
     if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1:
         raise KernelError("retention: q, k and v must be views of one projection with dense rows")
@@ -1421,17 +1430,158 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_sin: torch.
     _check(library().acv_retention(_p(q), _p(k), _p(v), q.stride(0), _p(cos_sin), rot, rows, _p(positions), _p(decay),
                                    float(k_scale), _p(state), _p(slots), _p(cu_q), _p(seg_seq), _p(seg_idx), seg_len,
                                    _p(seg), 1 if summaries else 0, _p(out), out.stride(0), n_items,
-                                   num_heads, dim, value_dim, dtype_code(q.dtype), _stream()), "retention")
+                                   num_heads, dim, value_dim, dtype_code(q.dtype), 1 if silu_inputs else 0, _stream()),
+           "retention")
     return out
 
 
 def retention_gate(o: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_heads: int, value_dim: int, eps: float,
-                   out_scale: float = 1.0) -> torch.Tensor:
-    """out = o / sqrt(mean over a head of o^2 + eps) * silu(gate) * out_scale; o float32, gate and out views of the run's type."""
+                   out_scale: float = 1.0, weight: torch.Tensor | None = None, joint: bool = False,
+                   gate_fn: str = "silu") -> torch.Tensor:
+    """out = o / sqrt(mean over a head of o^2 + eps) * silu(gate) * out_scale; o float32, gate and out views of the run's type.
+    ``joint``: the mean is taken over all heads side by side instead of each head by itself; ``weight`` (float32
+    [heads * value_dim]) multiplies the normed values; ``gate_fn`` "sigmoid" instead of "silu"."""
     _need_cuda(o, gate, out)
+    if weight is not None and (weight.dtype != torch.float32 or weight.numel() != num_heads * value_dim or not weight.is_contiguous()):
+        raise KernelError("retention_gate: the weight is a contiguous float32 vector over all heads' values")
+    if gate_fn not in ("silu", "sigmoid"):
+        raise KernelError(f"retention_gate: no gate function '{gate_fn}'")
     if o.dtype != torch.float32 or gate.dtype != out.dtype or gate.stride(1) != 1 or out.stride(1) != 1 or o.stride(1) != 1:
         raise KernelError("retention_gate: float32 o, and gate and out of one type with dense rows, are wanted")
     _check(library().acv_retention_gate(_p(o), o.stride(0), _p(gate), gate.stride(0), _p(out), out.stride(0), o.shape[0],
-                                        num_heads, value_dim, eps, float(out_scale), dtype_code(out.dtype), _stream()),
-           "retention_gate")
+                                        num_heads, value_dim, eps, float(out_scale), dtype_code(out.dtype), _p(weight),
+                                        1 if joint else 0, 1 if gate_fn == "sigmoid" else 0, _stream()), "retention_gate")
+    return out
+
+
+# ----------------------------------------------------------------------------- scores mixed across heads
+def distance_buckets(rows: int, far: float) -> tuple[torch.Tensor, int]:
+    """(bucket of each distance below the first one that reads the last row, int32 on the host; that last row).
+    A table of ``rows`` rows gives one row to each of the first rows/2 distances and spreads the rest evenly over the
+    logarithm of the distance up to ``far``; everything beyond reads the last row.  Computed in double precision."""
+    half = rows // 2
+    last = rows - 1
+    if half <= 0 or far <= half:
+        return torch.arange(min(max(half, 1), rows), dtype=torch.int32), last
+    out = []
+    n = 0
+    while True:
+        b = n if n < half else min(last, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+        if n >= half and b >= last:
+            break
+        out.append(b)
+        n += 1
+        if n > (1 << 22):
+            raise KernelError("distance_buckets: the table's last row is never reached")
+    return torch.tensor(out, dtype=torch.int32), last
+
+
+def attention_mixed(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                    positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                    num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
+                    table_rows: torch.Tensor | None = None, value_dim: int = 0, temp: torch.Tensor | None = None,
+                    softcap: float = 0.0, rel: torch.Tensor | None = None, bucket_of: torch.Tensor | None = None,
+                    last_row: int = 0, talk: torch.Tensor | None = None) -> torch.Tensor:
+    """Paged causal attention whose scores pass through more steps before the softmax: times ``temp`` [heads], a soft
+    cap, plus ``rel`` [rows, heads] by bucketed distance (``bucket_of`` int32 [distances], larger distances read
+    ``last_row``), then mixed across heads by ``talk`` [heads, heads]; each step optional.  Everything after the
+    score's product is float32; temp, rel and talk are float32 tensors."""
+    _need_cuda(q, out, k_pages)
+    for t in (temp, rel, talk):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise KernelError("attention_mixed: temp, rel and talk are contiguous float32 tensors")
+    n_dist = bucket_of.numel() if bucket_of is not None else 0
+    _check(library().acv_attention_mixed(
+        _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(positions), _p(seq_of_token),
+        _p(block_table), block_table.stride(0), _p(table_rows), q.shape[0], num_heads, num_kv_heads, head_dim,
+        int(value_dim) or head_dim, k_pages.shape[2], k_pages.shape[0], float(scale), int(window), _p(temp), float(softcap),
+        _p(rel), _p(bucket_of), n_dist, int(last_row), _p(talk), dtype_code(q.dtype), _stream()), "attention_mixed")
+    return out
+
+
+# ----------------------------------------------------------------------------- norms on both sides of a part
+def add_normed_rmsnorm(x: torch.Tensor, delta: torch.Tensor, weight_b: torch.Tensor, eps_b: float,
+                       weight: torch.Tensor | None, eps: float, out: torch.Tensor | None) -> torch.Tensor | None:
+    """The float32 stream x += delta / sqrt(mean(delta^2) + eps_b) * weight_b, in place; then, with ``out``,
+    out = x / sqrt(mean(x^2) + eps) * weight, rounded once to out's type.  delta: float32 or bfloat16."""
+    _need_cuda(x, delta)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not delta.is_contiguous() or delta.shape != x.shape \
+            or (out is not None and (not out.is_contiguous() or out.shape != x.shape)):
+        raise KernelError("add_normed_rmsnorm: a contiguous float32 stream, and delta and out of its shape, are wanted")
+    dtype = dtype_code(out.dtype) if out is not None else dtype_code(delta.dtype)
+    _check(library().acv_add_normed_rmsnorm(_p(x), _p(delta), dtype_code(delta.dtype), _p(weight_b), float(eps_b), _p(weight),
+                                            float(eps), _p(out), x.shape[0], x.shape[1], dtype, _stream()),
+           "add_normed_rmsnorm")
+    return out
+
+
+def cast_rows_f32(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r, :] = x[r, :] rounded to out's type; x float32 [rows, H], out a view [rows, H] with dense rows at any stride."""
+    _need_cuda(x, out)
+    if x.dtype != torch.float32 or x.shape != out.shape or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("cast_rows_f32: a float32 matrix and a view of its shape with dense rows are wanted")
+    _check(library().acv_cast_rows_f32(_p(x), x.stride(0), _p(out), out.stride(0), x.shape[0], x.shape[1],
+                                       dtype_code(out.dtype), _stream()), "cast_rows_f32")
+    return out
+
+
+ACTIVATIONS = {"xielu": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str, p0: float = 0.0, p1: float = 0.0) -> torch.Tensor:
+    """Elementwise, in float, rounded once.  "xielu": z > 0: p0 z^2 + z/2; z <= 0: p1 (exp(z) - 1 - z) + z/2;
+    "gelu_tanh"; "silu"."""
+    _need_cuda(x, out)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation: no kind '{kind}'; known: {', '.join(ACTIVATIONS)}")
+    if x.dtype != out.dtype or not x.is_contiguous() or not out.is_contiguous() or x.shape != out.shape:
+        raise KernelError("activation: contiguous input and output of one type and shape are wanted")
+    _check(library().acv_activation(_p(x), _p(out), x.numel(), ACTIVATIONS[kind], float(p0), float(p1), dtype_code(x.dtype),
+                                    _stream()), "activation")
+    return out
+
+
+# ----------------------------------------------------------------------------- attention through a kept latent
+def gemm_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[:, b, :] = a[:, b, :] @ w[b]^T for every b: a [M, B, K] and out [M, B, N] are views with dense last
+    dimension (any row and batch strides), w [B, N, K] contiguous; 32-bit accumulation on the CUDA cores."""
+    _need_cuda(a, w, out)
+    M, B, K = a.shape
+    N = w.shape[1]
+    if w.shape != (B, N, K) or out.shape != (M, B, N) or a.stride(2) != 1 or out.stride(2) != 1 or not w.is_contiguous() \
+            or a.dtype != w.dtype:
+        raise KernelError(f"gemm_batched: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    _check(library().acv_gemm_simt_batched(_p(a), a.stride(0), a.stride(1), _p(w), K, N * K, _p(out), out.stride(0),
+                                           out.stride(1), M, N, K, B, dtype_code(a.dtype), dtype_code(out.dtype), _stream()),
+           "gemm_batched")
+    return out
+
+
+def latent_prepare(q: torch.Tensor, q_out: torch.Tensor, kv: torch.Tensor, weight: torch.Tensor, eps: float,
+                   cos_sin: torch.Tensor | None, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                   block_table: torch.Tensor | None, pages: torch.Tensor | None, num_heads: int, dim: int, rot_dim: int,
+                   rank: int, table_rows: torch.Tensor | None = None) -> None:
+    """The kept row of every token, [normed latent | rotated shared key part], into its page, and every head's rotated
+    query part into ``q_out[:, h, rank:]`` (csrc/latent_attention.cu).  q: [T, heads*(dim+rot_dim)]; q_out:
+    [T, heads*(rank+rot_dim)]; kv: [T, rank+rot_dim]; pages [num_pages, 1, page_size, rank+rot_dim] or None."""
+    _need_cuda(q, q_out, kv)
+    if q.stride(1) != 1 or q_out.stride(1) != 1 or kv.stride(1) != 1 or q.dtype != kv.dtype or q_out.dtype != q.dtype:
+        raise KernelError("latent_prepare: q, q_out and kv have dense rows and one type")
+    rot = cos_sin.shape[1] if cos_sin is not None else 0
+    _check(library().acv_latent_prepare(
+        _p(q), q.stride(0), _p(q_out), q_out.stride(0), _p(kv), kv.stride(0), _p(weight), float(eps), _p(cos_sin), rot,
+        cos_sin.shape[0] if cos_sin is not None else 0, _p(positions), _p(seq_of_token), _p(block_table),
+        block_table.stride(0) if block_table is not None else 0, _p(table_rows), _p(pages),
+        pages.shape[2] if pages is not None else 1, pages.shape[0] if pages is not None else 0, q.shape[0], num_heads, dim,
+        rot_dim, rank, dtype_code(q.dtype), _stream()), "latent_prepare")
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out = x / sqrt(mean(x^2) + eps) * weight over each row, in float, rounded once; x and out [rows, H] views with
+    dense rows at any stride (a column range of a stacked projection's output)."""
+    _need_cuda(x, out)
+    if x.shape != out.shape or x.dtype != out.dtype or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("rmsnorm_rows: input and output views of one shape and type with dense rows are wanted")
+    _check(library().acv_rmsnorm_rows(_p(x), x.stride(0), _p(weight), float(eps), _p(out), out.stride(0), x.shape[0],
+                                      x.shape[1], dtype_code(x.dtype), _stream()), "rmsnorm_rows")
     return out

@@ -7,6 +7,7 @@ import torch
 from ..cache.manager import CachePlan
 from ..kernels import ops
 from ..parts import BLOCKS, CacheView, ModelPlan, Runtime, build
+from ..parts.blocks import NormedDelta, settle
 from ..parts.linear import Linear
 from ..weights.needs import TensorNeed
 
@@ -40,6 +41,8 @@ class DecoderModel:
             needs[plan.final_norm_prefix + name] = need
         for name, shape in plan.stream_vectors.items():
             needs[name] = TensorNeed(tuple(shape))
+        for name, shape in plan.stream_matrices.items():
+            needs[name] = TensorNeed(tuple(shape))
         # a tied head reads the embedding; a file that still carries the head's tensor is accepted
         needs[plan.head_name] = TensorNeed((plan.vocab_size, plan.hidden_size), "matrix", optional=plan.tied_head)
         return needs
@@ -55,6 +58,8 @@ class DecoderModel:
         self.final_norm.load({n[len(p):]: t for n, t in tensors.items() if n.startswith(p)}, rt)
         self.stream_vectors = {name: tensors[name].to(device=rt.device, dtype=torch.float32).contiguous()
                                for name in plan.stream_vectors}
+        self.stream_matrices = {name: Linear(tensors[name].to(device=rt.device, dtype=rt.dtype))
+                                for name in plan.stream_matrices}
         if plan.tied_head:
             self.head = Linear(self.embedding)  # the same storage, no copy
         else:
@@ -226,7 +231,17 @@ class DecoderModel:
         if not hasattr(self, "slot_leaves"):
             self.cache_plan()
         mult = 1.0
+        both = None
+        if any(e.stream_mix is not None for e in plan.schedule):
+            # [stream | embedding output] in the parts' element type: the right half is written once
+            H = plan.hidden_size
+            both = torch.empty((ctx.num_tokens, 2 * H), device=rt.device, dtype=rt.dtype)
+            ops.cast_rows_f32(x, both[:, H:])
         for e in plan.schedule:
+            if e.stream_mix is not None:
+                x, delta = settle(x, delta)
+                ops.cast_rows_f32(x, both[:, :plan.hidden_size])
+                x = self.stream_matrices[e.stream_mix](both, out_dtype=torch.float32)
             if e.stream_add is not None:
                 # a vector of the model joins the stream (the pending output of the layer before joins it later, in
                 # the next norm's kernel: the two sums commute)
@@ -237,6 +252,8 @@ class DecoderModel:
             mult = getattr(block, "residual_mult", 1.0)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, plan.vocab_size), device=rt.device, dtype=torch.float32)
+        if isinstance(delta, NormedDelta):
+            x, delta = settle(x, delta)
         kw = {"out_dtype": rt.dtype} if x.dtype != rt.dtype else {}
         if mult != 1.0:
             kw["delta_scale"] = mult        # the last layer's output joins the stream with its block's factor

@@ -153,3 +153,104 @@ class PreNormBlock:
             return x, a
         h = self.post_norm.forward(x, a, **kw, **scale)
         return x, self.feed_forward.forward(h, ctx)
+
+
+class NormedDelta:
+    """A part's output that has not joined the stream yet, with the norm it passes through on its way in:
+    x += tensor / sqrt(mean(tensor^2) + eps) * weight.  The sum is made by the kernel of whatever reads the stream
+    next (the next block's first norm), or by ``settle``."""
+
+    __slots__ = ("tensor", "weight", "eps")
+
+    def __init__(self, tensor: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+        self.tensor, self.weight, self.eps = tensor, weight, eps
+
+
+def settle(x: torch.Tensor, delta):
+    """(x, None) with whatever was pending added to the stream x."""
+    if isinstance(delta, NormedDelta):
+        ops.add_normed_rmsnorm(x, delta.tensor, delta.weight, delta.eps, None, 0.0, None)
+        return x, None
+    if delta is not None:
+        raise ValueError("settle: only an output with a norm of its own is added here; others join in the next norm")
+    return x, None
+
+
+@register("block", "sandwich")
+class SandwichBlock:
+    """x += norm_1b(mixer(norm_1(x))); x += norm_2b(feed_forward(norm_2(x))): an RMS norm in front of and behind each
+    part, over a float32 residual stream.  A part's output travels as a ``NormedDelta``: its norm, the sum into the
+    stream and the next part's input norm are one kernel (``ops.add_normed_rmsnorm``), so the stream is read and
+    written once per part.  The four norms are ``LayerSpec.norm`` (kind ``rmsnorm``) under the names
+    ``norm_prefixes`` (in front) and ``options["post_norms"]`` (behind)."""
+
+    residual_mult = 1.0
+
+    def __init__(self, spec: LayerSpec, hidden_size: int) -> None:
+        self.hidden_size = hidden_size
+        self.prefix = spec.prefix
+        self.pre_mixer, self.pre_ff = spec.norm_prefixes
+        self.post_mixer, self.post_ff = spec.options.get("post_norms", ("norm1b", "norm2b"))
+        has_ff = spec.feed_forward is not None
+        self.input_norm = build("norm", spec.norm, hidden_size)
+        self.mixer_out_norm = build("norm", spec.norm, hidden_size)
+        self.mixer = build("mixer", spec.mixer, hidden_size)
+        self.post_norm = build("norm", spec.norm, hidden_size) if has_ff else None
+        self.ff_out_norm = build("norm", spec.norm, hidden_size) if has_ff else None
+        self.feed_forward = build("feed_forward", spec.feed_forward, hidden_size) if has_ff else None
+        for n in (self.input_norm, self.mixer_out_norm, self.post_norm, self.ff_out_norm):
+            if n is not None and not (hasattr(n, "weight") and hasattr(n, "eps") and not hasattr(n, "bias")):
+                raise ValueError("the sandwich block is built for RMS norms")
+        self.run_dtype = None
+
+    def _norms(self):
+        return ((self.pre_mixer, self.input_norm), (self.post_mixer, self.mixer_out_norm), (self.pre_ff, self.post_norm),
+                (self.post_ff, self.ff_out_norm))
+
+    def tensor_needs(self):
+        needs = {}
+        for prefix, norm in self._norms():
+            if norm is not None:
+                for name, need in norm.tensor_needs().items():
+                    needs[prefix + name] = need
+        needs.update(self.mixer.tensor_needs())
+        if self.feed_forward is not None:
+            needs.update(self.feed_forward.tensor_needs())
+        return needs
+
+    def load(self, tensors, rt: Runtime) -> None:
+        self.run_dtype = rt.dtype
+        for prefix, norm in self._norms():
+            if norm is not None:
+                norm.load({n[len(prefix):]: t for n, t in tensors.items() if n.startswith(prefix)
+                           and n[len(prefix):] in norm.tensor_needs()}, rt)
+        self.mixer.load(tensors, rt)
+        if self.feed_forward is not None:
+            self.feed_forward.load(tensors, rt)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def weight_bytes(self) -> int:
+        parts = [n for _, n in self._norms()] + [self.mixer, self.feed_forward]
+        return sum(p.weight_bytes() for p in parts if p is not None)
+
+    def flops(self, num_tokens: int) -> float:
+        return self.mixer.flops(num_tokens) + (self.feed_forward.flops(num_tokens) if self.feed_forward is not None else 0.0)
+
+    def _enter(self, x, delta, norm):
+        """The pending output joins the stream; returns ``norm`` of the stream in the parts' element type."""
+        if isinstance(delta, NormedDelta):
+            out = torch.empty(x.shape, device=x.device, dtype=self.run_dtype)
+            return ops.add_normed_rmsnorm(x, delta.tensor, delta.weight, delta.eps, norm.weight, norm.eps, out)
+        return norm.forward(x, delta, out_dtype=self.run_dtype)
+
+    def forward(self, x, delta, ctx, cache: CacheView | None):
+        if x.dtype != torch.float32:
+            raise ValueError("the sandwich block is built for a float32 residual stream (ModelPlan.residual_dtype)")
+        h = self._enter(x, delta, self.input_norm)
+        a = NormedDelta(self.mixer.forward(h, ctx, cache), self.mixer_out_norm.weight, self.mixer_out_norm.eps)
+        if self.feed_forward is None:
+            return x, a
+        h = self._enter(x, a, self.post_norm)
+        return x, NormedDelta(self.feed_forward.forward(h, ctx), self.ff_out_norm.weight, self.ff_out_norm.eps)

@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..kernels import ops
@@ -248,3 +250,51 @@ class RoutedExperts(FeedForward):
             shared = self.shared_down(sact)
         out = torch.empty((T, H), device=dev, dtype=h.dtype)
         return ops.moe_combine(parts, place, top, shared, gate, out)
+
+
+@register("feed_forward", "dense")
+class DenseFF(FeedForward):
+    """y = W_down act(W_up x): two products and an activation between them, no gate.  ``activation``:
+
+        "xielu"      z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2, with the layer's two
+                     learned numbers (p, q) in the tensor ``names["act"]``, folded once at load in double precision
+        "gelu_tanh"  0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+        "silu"
+
+    computed in float on the product's output and rounded once."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "xielu", prefix: str = "mlp.",
+                 names: dict | None = None) -> None:
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"dense feed-forward: no activation '{activation}'; known: {', '.join(ops.ACTIVATIONS)}")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.activation = activation
+        self.prefix = prefix
+        self.names = {"up": "up", "down": "down", "act": "act", **(names or {})}
+        self.p0 = self.p1 = 0.0
+
+    def tensor_needs(self):
+        H, I = self.hidden_size, self.intermediate_size
+        needs = {self.prefix + self.names["up"]: TensorNeed((I, H)), self.prefix + self.names["down"]: TensorNeed((H, I))}
+        if self.activation == "xielu":
+            needs[self.prefix + self.names["act"]] = TensorNeed((2,))
+        return needs
+
+    def load(self, tensors, rt: Runtime) -> None:
+        w = lambda role: tensors[self.prefix + self.names[role]].to(device=rt.device, dtype=rt.dtype)
+        self.up, self.down = Linear(w("up")), Linear(w("down"))
+        if self.activation == "xielu":
+            p, q = (float(v) for v in tensors[self.prefix + self.names["act"]].to(torch.float64).cpu())
+            softplus = lambda z: math.log1p(math.exp(-abs(z))) + max(z, 0.0)
+            self.p0, self.p1 = softplus(p), 0.5 + softplus(q)
+
+    def weight_bytes(self) -> int:
+        return self.up.weight_bytes() + self.down.weight_bytes()
+
+    def flops(self, num_tokens: int) -> float:
+        return self.up.flops(num_tokens) + self.down.flops(num_tokens)
+
+    def forward(self, h, ctx):
+        z = self.up(h)
+        ops.activation(z, z, self.activation, self.p0, self.p1)
+        return self.down(z)

@@ -10,6 +10,7 @@ from ..weights.needs import TensorNeed
 from .base import CacheView, Mixer, Runtime, StepMetadata
 from .linear import Linear
 from .plan import PartSpec
+from .position import NoPosition
 from .registry import build, register
 
 
@@ -27,18 +28,39 @@ class Attention(Mixer):
     ``keep_first`` > 0 (with a window): the first ``keep_first`` tokens of a request stay visible to every later query,
     at their own positions.  ``names``: the four projections' tensor names behind ``prefix`` ({"q": name, ...}; biases
     are then read only under names given as "q.bias" ...).  ``out_scale``: a constant on the mixer's output, for a mixer
-    whose output enters a weighted sum; it is applied to the values as they are written to their pages."""
+    whose output enters a weighted sum; it is applied to the values as they are written to their pages.
+
+    ``qk_norm_weights`` False: q and k are brought to unit RMS and nothing else (no weight tensors).
+    ``score``: more steps between the score's product and the softmax, each optional, all 32-bit:
+        s_g = <q_g, k> * scale * temp[g]           "temp": tensor [heads]
+        s_g = cap * tanh(s_g / cap)                 "softcap": cap
+        s_g += rel[bucket(i - j)][g]                "rel": tensor [rows, heads] (rows: whatever the file holds), "far":
+                                                    the distance from which every key reads the last row; rows/2 single
+                                                    distances first, the rest spread evenly over ln(distance)
+        m_h = sum_g talk[h][g] s_g                  "talk": tensor [heads, heads]; the softmax is taken over m_h
+    (tensor names behind ``prefix``).  Such a layer runs ``ops.attention_mixed``."""
 
     ROLES = ("q", "k", "v", "o")
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, position: PartSpec,
                  qk_norm_eps: float | None = None, scale: float | None = None, window: int = 0,
                  prefix: str = "self_attn.", bias: bool | None = None, value_dim: int | None = None, keep_first: int = 0,
-                 names: dict | None = None, out_scale: float = 1.0) -> None:
+                 names: dict | None = None, out_scale: float = 1.0, qk_norm_weights: bool = True,
+                 score: dict | None = None) -> None:
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
         self.hidden_size = hidden_size
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
+        self.qk_norm_weights = bool(qk_norm_weights)
+        self.score = dict(score) if score else None
+        if self.score is not None:
+            unknown = set(self.score) - {"temp", "softcap", "rel", "far", "talk"}
+            if unknown or ("rel" in self.score) != ("far" in self.score):
+                raise ValueError(f"attention score steps: unknown {sorted(unknown)}, or 'rel' without 'far'")
+            if keep_first:
+                raise ValueError("attention: kept first tokens beside score steps are not built")
+        self.temp = self.rel = self.talk = self.bucket_of = None
+        self.rel_last = 0
         self.value_dim = int(value_dim) if value_dim else head_dim
         self.scale = float(scale) if scale is not None else head_dim ** -0.5
         self.qk_norm_eps = qk_norm_eps
@@ -81,9 +103,14 @@ class Attention(Mixer):
             needs[self.prefix + self.names[role]] = TensorNeed((n_out, n_in))
             if self.bias is not False and role + ".bias" in self.names:
                 needs[self.prefix + self.names[role + ".bias"]] = TensorNeed((n_out,), "bias", optional=self.bias is None)
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weights:
             needs[self.prefix + "q_norm.weight"] = TensorNeed((self.head_dim,), "norm")
             needs[self.prefix + "k_norm.weight"] = TensorNeed((self.head_dim,), "norm")
+        if self.score is not None:
+            NH = self.num_heads
+            for key, shape, role in (("temp", (NH,), "norm"), ("rel", (-1, NH), "matrix"), ("talk", (NH, NH), "matrix")):
+                if key in self.score:
+                    needs[self.prefix + self.score[key]] = TensorNeed(shape, role)
         for name, need in self.position.tensor_needs().items():
             needs[self.prefix + name] = need
         return needs
@@ -98,9 +125,19 @@ class Attention(Mixer):
         self.qkv = Linear.stacked([w("q"), w("k"), w("v")], [b("q"), b("k"), b("v")])
         self.o = Linear(w("o"), b("o"))
         self.q_norm = self.k_norm = None
-        if self.qk_norm_eps is not None:
-            f = lambda n: tensors[n].to(device=rt.device, dtype=torch.float32).contiguous()
+        f = lambda n: tensors[n].to(device=rt.device, dtype=torch.float32).contiguous()
+        if self.qk_norm_eps is not None and self.qk_norm_weights:
             self.q_norm, self.k_norm = f(self.prefix + "q_norm.weight"), f(self.prefix + "k_norm.weight")
+        elif self.qk_norm_eps is not None:
+            self.q_norm = self.k_norm = torch.ones(self.head_dim, device=rt.device, dtype=torch.float32)
+        if self.score is not None:
+            sc = self.score
+            self.temp = f(self.prefix + sc["temp"]) if "temp" in sc else None
+            self.talk = f(self.prefix + sc["talk"]) if "talk" in sc else None
+            if "rel" in sc:
+                self.rel = f(self.prefix + sc["rel"])
+                buckets, self.rel_last = ops.distance_buckets(self.rel.shape[0], float(sc["far"]))
+                self.bucket_of = buckets.to(rt.device)
         self.position.load({n[len(self.prefix):]: t for n, t in tensors.items() if n.startswith(self.prefix)}, rt)
 
     def decode_layer_spec(self):
@@ -117,7 +154,19 @@ class Attention(Mixer):
 
     # ---- cost of a step
     def extra_weight_bytes(self) -> int:
-        return sum(t.numel() * 4 for t in (self.q_norm, self.k_norm) if t is not None)
+        return sum(t.numel() * 4 for t in (self.q_norm, self.k_norm, self.temp, self.rel, self.talk) if t is not None)
+
+    def _attend(self, qkv, out, ctx, cache: CacheView, table) -> None:
+        """From normed, positioned queries (the first columns of ``qkv``) and the pages to the heads' outputs."""
+        NH, NKV, D, DV = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
+        if self.score is not None:
+            ops.attention_mixed(qkv, out, cache.k_pages, cache.v_pages, ctx.positions, ctx.seq_of_token, table, NH, NKV, D,
+                                self.scale, self.window, table_rows=ctx.table_rows, value_dim=DV, temp=self.temp,
+                                softcap=float(self.score.get("softcap", 0.0) or 0.0), rel=self.rel, bucket_of=self.bucket_of,
+                                last_row=self.rel_last, talk=self.talk)
+            return
+        ops.attention(qkv, out, cache.k_pages, cache.v_pages, ctx, table, NH, NKV, D, self.scale, self.window,
+                      work=ctx.work[self.metadata_key], value_dim=DV, keep_first=self.keep_first)
 
     def weight_bytes(self) -> int:
         return self.qkv.weight_bytes() + self.o.weight_bytes() + self.extra_weight_bytes()
@@ -153,6 +202,10 @@ class Attention(Mixer):
         if rotary is not None:
             ops.qk_norm_rope_append(qkv, NH, NKV, D, self.q_norm, self.k_norm, eps, rotary, ctx.positions,
                                     ctx.seq_of_token, table if kp is not None else None, kp, vp, table_rows=rows, **extra)
+        elif isinstance(self.position, NoPosition):
+            # nothing happens between norm and append: one launch for both
+            ops.qk_norm_rope_append(qkv, NH, NKV, D, self.q_norm, self.k_norm, eps, None, ctx.positions,
+                                    ctx.seq_of_token, table if kp is not None else None, kp, vp, table_rows=rows, **extra)
         else:
             if self.q_norm is not None:
                 ops.qk_norm_rope_append(qkv, NH, NKV, D, self.q_norm, self.k_norm, eps, None, ctx.positions,
@@ -163,12 +216,11 @@ class Attention(Mixer):
             if kp is not None:
                 ops.qk_norm_rope_append(qkv, NH, NKV, D, None, None, 0.0, None, ctx.positions, ctx.seq_of_token,
                                         table, kp, vp, table_rows=rows, **extra)
-        ops.attention(qkv, out, cache.k_pages, cache.v_pages, ctx, table, NH, NKV, D, self.scale, self.window,
-                      work=ctx.work[self.metadata_key], value_dim=DV, keep_first=self.keep_first)
+        self._attend(qkv, out, ctx, cache, table)
 
     def forward(self, h, ctx, cache: CacheView):
         NH, NKV, D = self.num_heads, self.num_kv_heads, self.head_dim
-        if self.value_dim != D or self.out_scale != 1.0:
+        if self.value_dim != D or self.out_scale != 1.0 or self.score is not None or isinstance(self.position, NoPosition):
             qkv = self.qkv(h)
             out = torch.empty((qkv.shape[0], self.inner_size), device=h.device, dtype=h.dtype)
             self.mix(qkv, ctx, cache, out)
@@ -408,3 +460,111 @@ class ParallelMixers(Mixer):
         l.mix(proj[:, :l.in_size], ctx, cache.parts.get("left"), inner[:, :l.inner_size])
         r.mix(proj[:, l.in_size:], ctx, cache.parts.get("right"), inner[:, l.inner_size:])
         return self.o(inner)
+
+
+@register("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    """Attention whose queries, keys and values pass through normed low-rank latents:
+
+        c_q = norm(W_dq h) w_dq,   q_h = W_uq,h c_q = [q_plain (dim) | q_rot (rot_dim)]
+        [c' | r'] = W_dkv h,        c = norm(c') w_dkv  (rank elements),   r = rot(r')  (rot_dim elements, one for all heads)
+        key_h = [W_uk,h c | r],     value_h = W_uv,h c,   score = scale <q_h, key_h> with q_rot rotated as r is
+
+    under a causal mask, with ``window`` > 0 limited to the last ``window`` keys; softmax; W_o over the heads.  rot
+    turns interleaved pairs (2i, 2i+1) of the first ``position.dim`` elements by position * theta^(-2i/dim).
+
+    Per token the layer keeps [c | r] and nothing else: one key/value head of rank + rot_dim elements whose values are
+    the first ``rank`` elements of the same rows.  The products with W_uk and W_uv are made on the query's side
+    (csrc/latent_attention.cu): the query that meets the kept rows is [W_uk,h^T q_plain | q_rot], and the weighted sum
+    of latents is projected by W_uv,h afterwards; both are one batched product over the heads.
+
+    Tensors behind ``prefix``: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, o (``names`` renames them); no biases."""
+
+    NAMES = {n: n for n in ("dq", "dq.norm", "uq", "dkv", "dkv.norm", "uk", "uv", "o")}
+
+    def __init__(self, hidden_size: int, num_heads: int, dim: int, rot_dim: int, value_dim: int, q_rank: int, kv_rank: int,
+                 scale: float | None, norm_eps: float, position: PartSpec, window: int = 0, prefix: str = "mix.",
+                 names: dict | None = None) -> None:
+        self.hidden_size = hidden_size
+        self.num_heads, self.dim, self.rot_dim, self.value_dim = num_heads, dim, rot_dim, value_dim
+        self.q_rank, self.kv_rank = q_rank, kv_rank
+        self.scale = float(scale) if scale is not None else (dim + rot_dim) ** -0.5
+        self.norm_eps = float(norm_eps)
+        self.window = int(window)
+        self.prefix = prefix
+        self.names = {**self.NAMES, **(names or {})}
+        self.position = build("position", position, hidden_size)
+        self.row = kv_rank + rot_dim            # elements of a kept row, and of a query that meets it
+
+    def _n(self, role: str) -> str:
+        return self.prefix + self.names[role]
+
+    def cache_need(self):
+        return PagedNeed(1, self.row, self.window, self.kv_rank, 0, 0, True)
+
+    def tensor_needs(self):
+        W, H, D, R, DV = self.hidden_size, self.num_heads, self.dim, self.rot_dim, self.value_dim
+        return {self._n("dq"): TensorNeed((self.q_rank, W)), self._n("dq.norm"): TensorNeed((self.q_rank,), "norm"),
+                self._n("uq"): TensorNeed((H * (D + R), self.q_rank)), self._n("dkv"): TensorNeed((self.row, W)),
+                self._n("dkv.norm"): TensorNeed((self.kv_rank,), "norm"), self._n("uk"): TensorNeed((H * D, self.kv_rank)),
+                self._n("uv"): TensorNeed((H * DV, self.kv_rank)), self._n("o"): TensorNeed((W, H * DV))}
+
+    def load(self, tensors, rt: Runtime) -> None:
+        w = lambda role: tensors[self._n(role)].to(device=rt.device, dtype=rt.dtype)
+        f = lambda role: tensors[self._n(role)].to(device=rt.device, dtype=torch.float32).contiguous()
+        H, D, DV, KR = self.num_heads, self.dim, self.value_dim, self.kv_rank
+        # both down projections read the same input: one stacked product, [c_q' | c' | r']
+        self.down = Linear.stacked([w("dq"), w("dkv")])
+        self.uq = Linear(w("uq"))
+        self.o = Linear(w("o"))
+        self.q_norm, self.kv_norm = f("dq.norm"), f("dkv.norm")
+        # per head: W_uk,h^T as the weight [rank, dim] of q_plain -> latent space; W_uv,h [value_dim, rank] as it is
+        self.uk_t = w("uk").view(H, D, KR).transpose(1, 2).contiguous()
+        self.uv = w("uv").view(H, DV, KR).contiguous()
+        self.position.load({}, rt)
+        if self.position.rotary_table() is None:
+            raise ValueError("latent_attention takes a position encoding that offers a rotary table")
+        if self.position.rotary_table().shape[1] > self.rot_dim:
+            raise ValueError("latent_attention: more rotated elements than the rotated part has")
+
+    # ---- cost of a step
+    def weight_bytes(self) -> int:
+        own = sum(t.numel() * t.element_size() for t in (self.uk_t, self.uv, self.q_norm, self.kv_norm))
+        return self.down.weight_bytes() + self.uq.weight_bytes() + self.o.weight_bytes() + own
+
+    def flops(self, num_tokens: int) -> float:
+        per_head = 2.0 * num_tokens * self.num_heads * self.kv_rank * (self.dim + self.value_dim)
+        return self.down.flops(num_tokens) + self.uq.flops(num_tokens) + self.o.flops(num_tokens) + per_head
+
+    def _seen(self, q: int, kv: int) -> float:
+        if self.window <= 0:
+            return q * (kv - q) + q * (q + 1) / 2
+        return float(sum(min(self.window, p + 1) for p in range(kv - q, kv)))
+
+    def mixing_flops(self, q_lens, kv_lens) -> float:
+        # scores over the kept rows, weighted sums over their latents
+        return 2.0 * self.num_heads * (self.row + self.kv_rank) * sum(self._seen(q, kv) for q, kv in zip(q_lens, kv_lens))
+
+    def cache_bytes_read(self, q_lens, kv_lens, itemsize: int) -> int:
+        keys = sum(min(kv, self.window + q - 1) if self.window > 0 else kv for q, kv in zip(q_lens, kv_lens))
+        return keys * self.row * itemsize
+
+    def forward(self, h, ctx, cache: CacheView):
+        H, D, R, DV, KR = self.num_heads, self.dim, self.rot_dim, self.value_dim, self.kv_rank
+        T = h.shape[0]
+        table = ctx.block_tables[cache.group]
+        down = self.down(h)                                     # [T, q_rank + rank + rot_dim]
+        cq = torch.empty((T, self.q_rank), device=h.device, dtype=h.dtype)
+        ops.rmsnorm_rows(down[:, :self.q_rank], self.q_norm, self.norm_eps, cq)
+        q = self.uq(cq)                                         # [T, H, dim + rot_dim]
+        met = torch.empty((T, H * self.row), device=h.device, dtype=h.dtype)      # the queries that meet the kept rows
+        ops.latent_prepare(q, met, down[:, self.q_rank:], self.kv_norm, self.norm_eps, self.position.rotary_table(),
+                           ctx.positions, ctx.seq_of_token, table if cache.writes else None,
+                           cache.k_pages if cache.writes else None, H, D, R, KR, table_rows=ctx.table_rows)
+        ops.gemm_batched(q.view(T, H, D + R)[:, :, :D], self.uk_t, met.view(T, H, self.row)[:, :, :KR])
+        lat = torch.empty((T, H * KR), device=h.device, dtype=h.dtype)            # weighted sums of latents
+        ops.attention_generic(met, lat, cache.k_pages, cache.k_pages, ctx.positions, ctx.seq_of_token, table, H, 1,
+                              self.row, self.scale, self.window, table_rows=ctx.table_rows, value_dim=KR)
+        out = torch.empty((T, H * DV), device=h.device, dtype=h.dtype)
+        ops.gemm_batched(lat.view(T, H, KR), self.uv, out.view(T, H, DV))
+        return self.o(out)

@@ -47,6 +47,9 @@ class ScheduleEntry:
     # (tensor name, row): that row of a [rows, hidden] tensor of the model joins the stream before this run
     # (a repeated stretch of layers that tells its passes apart by a vector of their own)
     stream_add: tuple[str, int] | None = None
+    # name of a [hidden, 2 hidden] matrix of the model: before this run the stream becomes W [x; x0], x0 being the
+    # embedding output (a repeated stretch of layers whose every pass starts from the stream and the input together)
+    stream_mix: str | None = None
 
 
 @dataclass(frozen=True)
@@ -71,6 +74,8 @@ class ModelPlan:
     logit_softcap: float = 0.0        # > 0: logits <- cap * tanh(logits / cap)
     # tensors of the model beside its layers', {name: shape}: what ``ScheduleEntry.stream_add`` names lives here
     stream_vectors: Mapping[str, tuple] = field(default_factory=dict)
+    # matrices of the model beside its layers', {name: shape}: what ``ScheduleEntry.stream_mix`` names lives here
+    stream_matrices: Mapping[str, tuple] = field(default_factory=dict)
 
     @property
     def num_cache_slots(self) -> int:

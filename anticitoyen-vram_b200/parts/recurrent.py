@@ -39,13 +39,23 @@ class Retention(SegmentedRecurrence):
     q and k get the position encoding (``position``; None: none), k is then multiplied by ``k_scale`` (default
     dim^-1/2).  Each head's o is brought to unit RMS (``norm_eps``, no weight), the heads side by side are multiplied
     by silu(W_g h) and by ``out_scale``, and projected by W_o.  Tensors behind ``prefix``: q, k, v, g, o (``names``
-    renames them); no biases."""
+    renames them); no biases.
+
+    Variants: ``input_act`` "silu": q, k and v are silu of their projections (in float, before anything else);
+    ``joint_norm``: the name of a weight over all heads' values: the heads side by side are then normed together,
+    o / sqrt(mean over all heads of o^2 + eps) * weight, instead of each head to unit RMS; ``gate_fn`` "sigmoid"
+    instead of "silu"."""
 
     NAMES = {n: n for n in ("q", "k", "v", "g", "o")}
 
     def __init__(self, hidden_size: int, num_heads: int, dim: int, value_dim: int, decay, norm_eps: float,
                  position: PartSpec | None = None, k_scale: float | None = None, prefix: str = "mix.",
-                 names: dict | None = None, out_scale: float = 1.0) -> None:
+                 names: dict | None = None, out_scale: float = 1.0, input_act: str | None = None,
+                 joint_norm: str | None = None, gate_fn: str = "silu") -> None:
+        if input_act not in (None, "silu") or gate_fn not in ("silu", "sigmoid"):
+            raise ValueError(f"retention: input_act {input_act!r} / gate_fn {gate_fn!r} are not built")
+        self.input_act, self.joint_norm, self.gate_fn = input_act, joint_norm, gate_fn
+        self.norm_weight = None
         decay = [float(d) for d in decay]
         if len(decay) != num_heads:
             raise ValueError(f"{len(decay)} decays for {num_heads} heads")
@@ -70,25 +80,30 @@ class Retention(SegmentedRecurrence):
 
     def tensor_needs(self):
         H = self.hidden_size
-        return {self._n("q"): TensorNeed((self.qk_size, H)), self._n("k"): TensorNeed((self.qk_size, H)),
-                self._n("v"): TensorNeed((self.inner_size, H)), self._n("g"): TensorNeed((self.inner_size, H)),
-                self._n("o"): TensorNeed((H, self.inner_size))}
+        needs = {self._n("q"): TensorNeed((self.qk_size, H)), self._n("k"): TensorNeed((self.qk_size, H)),
+                 self._n("v"): TensorNeed((self.inner_size, H)), self._n("g"): TensorNeed((self.inner_size, H)),
+                 self._n("o"): TensorNeed((H, self.inner_size))}
+        if self.joint_norm is not None:
+            needs[self.prefix + self.joint_norm] = TensorNeed((self.inner_size,), "norm")
+        return needs
 
     def load(self, tensors, rt: Runtime) -> None:
         w = lambda role: tensors[self._n(role)].to(device=rt.device, dtype=rt.dtype)
         self.qkv = Linear.stacked([w("q"), w("k"), w("v"), w("g")])
         self.o = Linear(w("o"))
         self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=rt.device)
+        if self.joint_norm is not None:
+            self.norm_weight = tensors[self.prefix + self.joint_norm].to(device=rt.device, dtype=torch.float32).contiguous()
         if self.position is not None:
             self.position.load({}, rt)
             if self.position.rotary_table() is None:
                 raise ValueError("retention takes a position encoding that offers a rotary table")
 
     def extra_weight_bytes(self) -> int:
-        return 0
+        return self.norm_weight.numel() * 4 if self.norm_weight is not None else 0
 
     def weight_bytes(self) -> int:
-        return self.qkv.weight_bytes() + self.o.weight_bytes()
+        return self.qkv.weight_bytes() + self.o.weight_bytes() + self.extra_weight_bytes()
 
     def flops(self, num_tokens: int) -> float:
         return self.qkv.flops(num_tokens) + self.o.flops(num_tokens)
@@ -107,8 +122,9 @@ class Retention(SegmentedRecurrence):
         table = self.position.rotary_table() if self.position is not None else None
         ops.retention(proj[:, :a], proj[:, a:b], proj[:, b:b + self.inner_size], table, ctx.positions, self.decay,
                       self.k_scale, cache.state, ctx.state_slots[cache.group], ctx.cu_q, ctx.num_seqs, o, H, D, DV,
-                      work=ctx.work.get(self.metadata_key))
-        ops.retention_gate(o, proj[:, b + self.inner_size:], out, H, DV, self.norm_eps, self.out_scale)
+                      work=ctx.work.get(self.metadata_key), silu_inputs=self.input_act == "silu")
+        ops.retention_gate(o, proj[:, b + self.inner_size:], out, H, DV, self.norm_eps, self.out_scale,
+                           weight=self.norm_weight, joint=self.joint_norm is not None, gate_fn=self.gate_fn)
 
     def forward(self, h, ctx, cache: CacheView):
         proj = self.qkv(h)

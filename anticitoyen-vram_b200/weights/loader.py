@@ -76,7 +76,7 @@ def load_tensors(folder: str | os.PathLike, needs: Mapping[str, TensorNeed],
         missing = [n for n, need in needs.items() if n not in present and not need.optional]
         unexpected = sorted(n for n in present if n not in needs)
         wrong_shape = [(n, present[n][1], need.shape) for n, need in needs.items()
-                       if n in present and present[n][1] != tuple(need.shape)]
+                       if n in present and not need.fits(present[n][1])]
         if missing or wrong_shape or (unexpected and strict):
             raise WeightError(folder, missing, unexpected, wrong_shape)
         if unexpected:

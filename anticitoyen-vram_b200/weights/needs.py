@@ -12,11 +12,23 @@ class TensorNeed:
     ``role`` decides the random initialisation ("matrix", "embedding" and "bias":
     N(0, 0.02); "norm": 1 + N(0, 0.1); "table": integers) and nothing else;
     ``optional`` tensors may be absent from the file (a tied output head).
+    A dimension written -1 is the file's to choose (a table whose number of rows no
+    configuration key names: the part reads it from the tensor it is given); a
+    random model gives such a dimension ``free_size``.
     """
 
     shape: tuple[int, ...]
     role: str = "matrix"
     optional: bool = False
+    free_size: int = 32
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w == g or (w == -1 and g >= 1) for w, g in zip(self.shape, shape))
+
+    @property
+    def concrete_shape(self) -> tuple[int, ...]:
+        return tuple(self.free_size if d == -1 else d for d in self.shape)
 
 
 class WeightError(ValueError):

@@ -88,8 +88,9 @@ def normal_of_words(words: np.ndarray) -> np.ndarray:
 
 
 def _host_tensor(need: TensorNeed, key: int, dtype: torch.dtype) -> torch.Tensor:
+    shape = need.concrete_shape
     n = 1
-    for d in need.shape:
+    for d in shape:
         n *= d
     chunk = 1 << 20                              # counters per pass: a few tens of MB of temporaries
     if need.role == "table":
@@ -105,7 +106,7 @@ def _host_tensor(need: TensorNeed, key: int, dtype: torch.dtype) -> torch.Tensor
             out[lo:hi] = (words[:hi - lo] & np.uint32(0x7FFF)).astype(np.int32)
         else:
             out[lo:hi] = np.float32(mean) + np.float32(std) * normal_of_words(words[:hi - lo])
-    t = torch.from_numpy(out).view(need.shape)
+    t = torch.from_numpy(out).view(shape)
     return t if need.role == "table" else t.to(dtype)
 
 
@@ -114,12 +115,13 @@ def _device_tensor(need: TensorNeed, key: int, device: torch.device, dtype: torc
     tables = _DEVICE_TABLES.get(str(device))
     if tables is None:
         tables = _DEVICE_TABLES[str(device)] = tuple(torch.from_numpy(t).to(device) for t in quantile_tables())
+    shape = need.concrete_shape
     if need.role == "table":
-        return ops.random_int(torch.empty(need.shape, device=device, dtype=torch.int32), key, 0x7FFF)
+        return ops.random_int(torch.empty(shape, device=device, dtype=torch.int32), key, 0x7FFF)
     mean, std = (1.0, 0.1) if need.role == "norm" else (0.0, 0.02)
     if dtype not in (torch.float32, torch.bfloat16):
-        return ops.random_normal(torch.empty(need.shape, device=device, dtype=torch.float32), key, mean, std, *tables).to(dtype)
-    return ops.random_normal(torch.empty(need.shape, device=device, dtype=dtype), key, mean, std, *tables)
+        return ops.random_normal(torch.empty(shape, device=device, dtype=torch.float32), key, mean, std, *tables).to(dtype)
+    return ops.random_normal(torch.empty(shape, device=device, dtype=dtype), key, mean, std, *tables)
 
 
 def random_tensor(name: str, need: TensorNeed, seed: int, device: str | torch.device = "cpu",
