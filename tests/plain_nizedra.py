@@ -64,12 +64,12 @@ def mixed_heads_attention(h, w, pre, m, eps):
     q, k = rms_norm(q, eps), rms_norm(k, eps)
     rel, talk, temp = w[pre + "rel"], w[pre + "talk"], w[pre + "temp"]
     rows = rel.shape[0]
-    cap = m["softcap"]
+    cap = m.get("softcap")        # absent: no cap
     buckets = np.array([[distance_bucket(i - j, rows, m["bias_max"]) if j <= i else 0 for j in range(T)] for i in range(T)])
     s = np.zeros((H, T, T))
     for g in range(H):
         raw = q[:, g, :] @ k[:, g // (H // G), :].T * m["scale"] * temp[g]
-        s[g] = cap * np.tanh(raw / cap) + rel[buckets, g]
+        s[g] = (cap * np.tanh(raw / cap) if cap else raw) + rel[buckets, g]
     s = np.einsum("hg,gij->hij", talk, s)
     visible = np.tril(np.ones((T, T), dtype=bool))
     out = np.zeros((T, H, DV))
@@ -177,3 +177,11 @@ def forward(cfg, w, tokens, streams=None):
         if streams is not None:
             streams.append(x.copy())
     return rms_norm(x, cfg["norm"]["eps"], w["final.norm"]) @ w["head"].T
+
+
+def greedy(cfg, w, prompt, n):
+    """The n tokens that follow ``prompt`` when the most probable token is taken every time."""
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(np.argmax(forward(cfg, w, ids)[-1])))
+    return ids[len(prompt):]
