@@ -312,6 +312,103 @@ REDUDRA_SIZES = {
               channels=4096, blocks=16, taps=4, ff=12288),
 }
 
+NIZEDRA_SIZES = {
+    # width; attention: heads, kv heads, head size (keys and values), where the distance-bias table ends (32 rows);
+    # lightning: heads, key size, value size; latent attention: heads, unrotated and rotated key size, value size, ranks
+    # of the query and key/value latents, window; feed-forward size (two matrices: 3/2 of the gated relative's three)
+    "s": dict(width=2048, heads=16, kv_heads=4, dim=128, bias_max=4096, l_heads=16, l_dim=128, l_vdim=128,
+              m_heads=16, m_dim=64, m_rot=64, m_vdim=128, q_rank=768, kv_rank=512, window=1024, ff=9216),
+    "m": dict(width=4096, heads=32, kv_heads=8, dim=128, bias_max=4096, l_heads=32, l_dim=128, l_vdim=128,
+              m_heads=32, m_dim=64, m_rot=64, m_vdim=128, q_rank=1536, kv_rank=512, window=2048, ff=18432),
+}
+
+
+def run_nizedra(args) -> int:
+    """``--design nizedra``: prefill and decode throughput of the Nizedra design at layer sizes of real models (random
+    weights; six layers: mixed-heads attention, lightning, latent attention, twice), beside a Qwen3 model of equal size:
+    the same width, as many attention heads of the same size, a gated feed-forward with as many weights.  Whole steps
+    through the step function, and the mixer and feed-forward of each kind of layer alone with their rooflines (L2
+    flushed before each timed run).  One JSON line."""
+    import torch
+
+    from acvram_b200 import bench as B
+    from acvram_b200.config import NizedraConfig, Qwen3Config
+    from acvram_b200.engine.runner import ModelRunner
+    from acvram_b200.models import build_random
+
+    pk, pk_src = peaks()
+    K, W = args.steps, args.warmup
+    page = 64
+    layers, vocab = args.layers or 6, 32768
+    out = {"design": "nizedra", "beside": "qwen3", "layers": layers, "vocab": vocab, "dtype": "bf16", "page_size": page,
+           "data": "synthetic token ids, random weights", "peaks": {**pk, "source": pk_src}, "sizes": {}}
+    for name in args.sizes.split(","):
+        z = NIZEDRA_SIZES[name]
+        mlp = {"kind": "dense", "ff": z["ff"]}
+        att = {"type": "attention", "mlp": mlp, "mixer": {
+            "heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5 * 8.0,
+            "softcap": 50.0, "bias_max": z["bias_max"]}}
+        lig = {"type": "lightning", "mlp": mlp, "mixer": {
+            "heads": z["l_heads"], "dim": z["l_dim"], "vdim": z["l_vdim"],
+            "decay": [1.0 - 2.0 ** (-5 - 3 * h / z["l_heads"]) for h in range(z["l_heads"])]}}
+        lat = {"type": "latent_attention", "mlp": mlp, "mixer": {
+            "heads": z["m_heads"], "dim": z["m_dim"], "rot_dim": z["m_rot"], "vdim": z["m_vdim"], "q_rank": z["q_rank"],
+            "kv_rank": z["kv_rank"], "scale": (z["m_dim"] + z["m_rot"]) ** -0.5, "mask": {"size": z["window"]},
+            "rot": {"base": 1e6, "dims": z["m_rot"]}}}
+        kinds3 = (att, lig, lat)
+        ncfg = NizedraConfig.from_dict({"architecture": "Nizedra", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6},
+                                        "layers": [kinds3[i % 3] for i in range(layers)]})
+        qcfg = Qwen3Config(vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"] * 2 // 3, num_hidden_layers=layers,
+                           num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                           rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=8192, tie_word_embeddings=False)
+        res = {"nizedra": dict(z), "qwen3": {"hidden": qcfg.hidden_size, "intermediate": qcfg.intermediate_size,
+                                            "q_heads": qcfg.num_attention_heads, "kv_heads": qcfg.num_key_value_heads,
+                                            "head_dim": qcfg.head_dim}}
+        for arm, cfg in (("nizedra", ncfg), ("qwen3", qcfg)):
+            model = build_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0")
+            batch_max = 64
+            tokens = batch_max * (args.context + 2 * (K + W) + 2 * page) + 4096
+            runner = ModelRunner(model, page, tokens // page + 8, batch_max + 2, max_len=8192)
+            if not args.no_cuda_graphs:
+                runner.enable_graphs()
+            r = {"weights_gb": round(model.weight_bytes() / 1e9, 3)}
+            try:
+                pre = B.time_prefill(runner, 2048, reps=5, warmup=3)
+                flops = B.prefill_flops(model, 2048)
+                r["prefill_2048"] = {"tokens_per_s": round(pre["tokens_per_s"], 1), "ms": round(pre["ms"], 3),
+                                     "tflops_frac": round(flops / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+                for b in (8, 64):
+                    names = [f"d{b}-{i}" for i in range(b)]
+                    B.fill_contexts(runner, names, args.context)
+                    try:
+                        d = B.time_decode(runner, names, K, W)
+                    finally:
+                        for n in names:
+                            runner.release(n)
+                    nbytes = B.decode_step_bytes(model, b, args.context + W + K // 2)
+                    r[f"decode_b{b}"] = {"tokens_per_s": round(d["tokens_per_s"], 1), "ms_per_step": round(d["ms_per_step"], 4),
+                                         "hbm_frac": round(nbytes / (d["ms_per_step"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+                kinds = (("attention", 0), ("lightning", 1), ("latent", 2)) if arm == "nizedra" and layers > 2 else (("", 0),)
+                for kind, layer in kinds:
+                    for label, ql, kl in (("prefill_2048", [2048], [2048]), ("decode_b64", [1] * 64, [args.context] * 64)):
+                        parts = B.time_parts(runner, ql, kl, layer=layer)
+                        for part, v in parts.items():
+                            if part == "feed_forward" and layer:
+                                continue        # every layer's feed-forward is the same
+                            sec = v["ms"] * 1e-3
+                            r[f"{kind + '_' if kind else ''}{part}_{label}"] = {
+                                "us": round(v["ms"] * 1e3, 1),
+                                "tflops_frac": round(v["flops"] / sec / (pk["bf16_tflops"] * 1e12), 4),
+                                "hbm_frac": round(v["bytes"] / sec / 1e9 / pk["hbm_gbs"], 4)}
+            except B.Refused as exc:
+                r["refused"] = str(exc)
+            res[arm + "_result"] = r
+            del runner, model
+            _free_device_memory()
+        out["sizes"][name] = res
+    print(json.dumps(out))
+    return 0
+
 
 def run_redudra(args) -> int:
     """``--design redudra``: prefill and decode throughput of the Redudra design at layer sizes of real models (random
@@ -498,7 +595,7 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16, help="tokens in a page of the cache (the engine's own default is 64)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-cuda-graphs", action="store_true")
-    ap.add_argument("--design", default="", choices=["", "zotonex", "redudra"],
+    ap.add_argument("--design", default="", choices=["", "zotonex", "redudra", "nizedra"],
                     help="measure another design beside its closest relative instead of the headline (see run_design)")
     ap.add_argument("--sizes", default="s,m", help="with --design: which of its sizes (s: width 2048, m: width 4096)")
     ap.add_argument("--time-limit", type=float, default=240.0,
@@ -513,6 +610,8 @@ def main() -> int:
         return run_reference(args)
     if args.design == "redudra":
         return run_redudra(args)
+    if args.design == "nizedra":
+        return run_nizedra(args)
     if args.design:
         return run_design(args)
     return run_ours(args)
