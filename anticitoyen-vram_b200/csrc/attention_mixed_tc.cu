@@ -1,0 +1,409 @@
+// Head-mixing attention (see attention_mixed.cu for the score steps) on the tensor cores, bfloat16 pages and queries.
+//
+// The softmax of head h at (query i, key j) needs every head's score of that pair, so the unit of work is a tile of 16
+// query tokens of one request with ALL heads: one warp a head, 16 x BN scores a warp and key tile on mma.sync m16n8k16
+// (float accumulation).  Each warp leaves its scores, after temp, soft cap and distance bias (all float), in shared
+// memory; after a barrier warp h mixes its row of `talk` over them straight into the accumulator layout of the tile,
+// masks, runs the online softmax and multiplies the weights (rounded to bfloat16 as the other tensor-core attention
+// kernels do) with its kv-head's values.
+//
+// More than 16 heads: the tile is shared by a thread-block cluster of 2 or 4 CTAs, each with NH / cluster heads (and
+// the key/value heads those read); the mix reads the other CTAs' scores through distributed shared memory and the two
+// barriers around the scores become cluster barriers.
+//
+// Keys and values arrive by cp.async, one buffer each: the next key tile is fetched while the mix, softmax and value
+// product of this one run (its buffer is free once the scores are written), the next value tile while the next
+// scores are computed.  Rows are padded by 16 bytes instead of swizzled, so head sizes need only be multiples of 8
+// (zero-filled to the next multiple of 16 in shared memory).
+//
+// Work: `n_tiles` tiles of 128 query tokens from the step's work list, each cut into 8 sub-tiles of 16, then `n_dec`
+// requests with one token each (a sub-tile with one row).
+#include "mma_tiles.cuh"
+
+#define MT_ROWS 16
+#define MT_SUB 8            // sub-tiles in a work-list tile of 128 tokens
+#define MT_MAX_WARPS 16
+#define MT_LOG2E 1.4426950408889634f
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ float2 ld_cluster_f2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+    return v;
+}
+
+struct MixedArgs {
+    const bf16* q; int q_stride; bf16* out; int out_stride;
+    const bf16* k_pages; const bf16* v_pages;
+    const int* tile_seq; const int* tile_q0; int n_tiles;
+    const int* dec_tokens; const int* dec_seqs; int n_dec;
+    const int* cu_q; const int* kv_len;
+    const int* block_table; int bt_stride; const int* bt_rows;
+    int NH, NKV, D, DV, page_size, num_pages;
+    float scale; int window;
+    const float* temp; float cap; const float* rel; const int* bucket_of; int n_dist, last_row, rel_rows;
+    const float* talk;
+    int cl;                 // CTAs in a cluster (1, 2 or 4)
+};
+
+template <int BN, int NDV>
+__global__ void __launch_bounds__(MT_MAX_WARPS * 32)
+attn_mixed_tc_kernel(const MixedArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int NH = a.NH, NKV = a.NKV, D = a.D, DV = a.DV;
+    const int cl = a.cl;
+    const int HPC = NH / cl;                    // heads of this CTA = its warps
+    const int DP = (D + 15) & ~15, DVP = (DV + 15) & ~15;
+    const int QP = DP * 2 + 16, VP = DVP * 2 + 16;          // row pitches in bytes
+    const int SP = BN + 8;                                   // floats in a row of scores
+    const int rank = cl > 1 ? (int)cluster_rank() : 0;
+    const int h_first = rank * HPC;
+    const int group = NH / NKV;
+    const int kv_first = h_first / group;
+    const int n_kv = (h_first + HPC - 1) / group - kv_first + 1;    // the same in every CTA: the launcher sees to it
+    const int n_kv_max = n_kv;
+
+    unsigned char* q_s = smem;                                              // [HPC][16][QP]
+    unsigned char* k_s = q_s + (size_t)HPC * MT_ROWS * QP;                  // [n_kv][BN][QP]
+    unsigned char* v_s = k_s + (size_t)n_kv_max * BN * QP;                  // [n_kv][BN][VP]
+    float* s_s = reinterpret_cast<float*>(v_s + (size_t)n_kv_max * BN * VP);    // [HPC][16][SP]
+    float* tk_s = s_s + (size_t)HPC * MT_ROWS * SP;                         // [HPC][NH]: rows of talk of this CTA's heads
+    float* rel_s = tk_s + (size_t)HPC * NH;                                 // [rel_rows][NH]
+
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthr = blockDim.x;
+    const int unit = blockIdx.x / cl;
+    int seq, tok0, rows, pos0;
+    if (unit < a.n_tiles * MT_SUB) {
+        const int tile = unit / MT_SUB;
+        seq = a.tile_seq[tile];
+        const int q0 = a.tile_q0[tile] + (unit % MT_SUB) * MT_ROWS;
+        const int q_len = a.cu_q[seq + 1] - a.cu_q[seq];
+        if (q0 >= q_len) return;                 // the same for every CTA of the cluster
+        tok0 = a.cu_q[seq] + q0;
+        rows = min(MT_ROWS, q_len - q0);
+        pos0 = a.kv_len[seq] - q_len + q0;
+    } else {
+        const int i = unit - a.n_tiles * MT_SUB;
+        seq = a.dec_seqs[i];
+        tok0 = a.dec_tokens[i];
+        rows = 1;
+        pos0 = a.kv_len[seq] - 1;
+    }
+    const int h = h_first + warp;
+    const int kv_local = h / group - kv_first;
+    if (pos0 < 0) {                              // a padded slot of a captured batch: nothing is kept for it
+        for (int e = lane; e < DV; e += 32) a.out[(size_t)tok0 * a.out_stride + (size_t)h * DV + e] = from_f32<bf16>(0.f);
+        return;
+    }
+    const int* bt = a.block_table + (size_t)(a.bt_rows ? a.bt_rows[seq] : seq) * a.bt_stride;
+    const int window = a.window;
+    const int hi = pos0 + rows - 1;
+    const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int j_first = lo & ~(BN - 1);
+    const int n_t = (hi - j_first) / BN + 1;
+    const int CH = DP / 8, CHV = DVP / 8;
+
+    // queries of all local heads, the talk rows, the bias table
+    for (int id = tid; id < HPC * MT_ROWS * CH; id += nthr) {
+        const int c = id % CH, r = (id / CH) % MT_ROWS, w = id / (CH * MT_ROWS);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows && c * 8 < D)
+            v = *reinterpret_cast<const uint4*>(a.q + (size_t)(tok0 + r) * a.q_stride + (size_t)(h_first + w) * D + c * 8);
+        *reinterpret_cast<uint4*>(q_s + ((size_t)w * MT_ROWS + r) * QP + c * 16) = v;
+    }
+    for (int id = tid; id < HPC * NH; id += nthr) {
+        const int w = id / NH, g = id % NH;
+        tk_s[id] = a.talk ? a.talk[(size_t)(h_first + w) * NH + g] : (g == h_first + w ? 1.f : 0.f);
+    }
+    if (a.rel)
+        for (int id = tid; id < a.rel_rows * NH; id += nthr) rel_s[id] = a.rel[id];
+
+    auto load_keys = [&](int t) {
+        const int j0 = j_first + t * BN;
+        for (int id = tid; id < n_kv * BN * CH; id += nthr) {
+            const int c = id % CH, r = (id / CH) % BN, kvl = id / (CH * BN);
+            const int j = j0 + r;
+            bool ok = j <= hi && j >= lo && c * 8 < D;
+            size_t off = 0;
+            if (ok) {
+                const int pg = bt[j / a.page_size];
+                ok = pg >= 0 && pg < a.num_pages;
+                off = (((size_t)pg * NKV + kv_first + kvl) * a.page_size + (j % a.page_size)) * D + c * 8;
+            }
+            cp_async16(smem_u32(k_s + ((size_t)kvl * BN + r) * QP + c * 16), ok ? (const void*)(a.k_pages + off) : (const void*)a.k_pages, ok);
+        }
+    };
+    auto load_values = [&](int t) {
+        const int j0 = j_first + t * BN;
+        for (int id = tid; id < n_kv * BN * CHV; id += nthr) {
+            const int c = id % CHV, r = (id / CHV) % BN, kvl = id / (CHV * BN);
+            const int j = j0 + r;
+            bool ok = j <= hi && j >= lo && c * 8 < DV;
+            size_t off = 0;
+            if (ok) {
+                const int pg = bt[j / a.page_size];
+                ok = pg >= 0 && pg < a.num_pages;
+                off = (((size_t)pg * NKV + kv_first + kvl) * a.page_size + (j % a.page_size)) * DV + c * 8;
+            }
+            cp_async16(smem_u32(v_s + ((size_t)kvl * BN + r) * VP + c * 16), ok ? (const void*)(a.v_pages + off) : (const void*)a.v_pages, ok);
+        }
+    };
+    load_keys(0);
+    cp_async_commit();
+    load_values(0);
+    cp_async_commit();
+
+    const int mi = lane >> 3, lr = lane & 7;
+    const int r_lo = lane >> 2, c_lo = (lane & 3) * 2;
+    const int p_row[2] = {pos0 + r_lo, pos0 + r_lo + 8};
+    const int lo_row[2] = {window > 0 ? max(0, p_row[0] - window + 1) : 0, window > 0 ? max(0, p_row[1] - window + 1) : 0};
+    const float qk_scale = a.scale * (a.temp ? a.temp[h] : 1.f);
+    const float cap = a.cap, inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
+    const uint32_t qb = smem_u32(q_s + (size_t)warp * MT_ROWS * QP);
+    const uint32_t kb = smem_u32(k_s + (size_t)kv_local * BN * QP);
+    const uint32_t vb = smem_u32(v_s + (size_t)kv_local * BN * VP);
+    float* s_own = s_s + (size_t)warp * MT_ROWS * SP;
+    const uint32_t s_base = smem_u32(s_s);
+
+    float acc[2 * NDV][4];
+#pragma unroll
+    for (int i = 0; i < 2 * NDV; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    for (int t = 0; t < n_t; ++t) {
+        const int j0 = j_first + t * BN;
+        cp_async_wait<1>();                     // this tile's keys (its values may still be on their way)
+        __syncthreads();
+        float s[BN / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+        for (int kd = 0; kd < DP / 16; ++kd) {
+            uint32_t qf[4];
+            ldmatrix_x4(qf, qb + ((mi & 1) * 8 + lr) * QP + (kd * 2 + (mi >> 1)) * 16);
+#pragma unroll
+            for (int np = 0; np < BN / 16; ++np) {
+                uint32_t b[4];
+                ldmatrix_x4(b, kb + (np * 16 + (mi >> 1) * 8 + lr) * QP + (kd * 2 + (mi & 1)) * 16);
+                mma_bf16(s[2 * np], qf, b[0], b[1]);
+                mma_bf16(s[2 * np + 1], qf, b[2], b[3]);
+            }
+        }
+        // this head's steps on its own scores, then into shared memory for every head's mix
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float x = s[nt][e] * qk_scale;
+                if (cap > 0.f) x = cap * tanhf(x * inv_cap);
+                if (a.rel) {
+                    const int dist = p_row[e >> 1] - (j0 + nt * 8 + c_lo + (e & 1));
+                    if (dist >= 0) x += rel_s[(dist < a.n_dist ? a.bucket_of[dist] : a.last_row) * NH + h];
+                }
+                s[nt][e] = x;
+            }
+            *reinterpret_cast<float2*>(s_own + r_lo * SP + nt * 8 + c_lo) = make_float2(s[nt][0], s[nt][1]);
+            *reinterpret_cast<float2*>(s_own + (r_lo + 8) * SP + nt * 8 + c_lo) = make_float2(s[nt][2], s[nt][3]);
+        }
+        if (cl > 1) cluster_barrier(); else __syncthreads();       // every head's scores are there; the key buffer is free
+        if (t + 1 < n_t) load_keys(t + 1);
+        cp_async_commit();
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+        const float* tk = tk_s + (size_t)warp * NH;
+        if (cl == 1) {
+            for (int g = 0; g < NH; ++g) {
+                const float w = tk[g];
+                const float* sg = s_s + (size_t)g * MT_ROWS * SP + r_lo * SP + c_lo;
+#pragma unroll
+                for (int nt = 0; nt < BN / 8; ++nt) {
+                    const float2 u = *reinterpret_cast<const float2*>(sg + nt * 8);
+                    const float2 v = *reinterpret_cast<const float2*>(sg + 8 * SP + nt * 8);
+                    s[nt][0] = fmaf(w, u.x, s[nt][0]); s[nt][1] = fmaf(w, u.y, s[nt][1]);
+                    s[nt][2] = fmaf(w, v.x, s[nt][2]); s[nt][3] = fmaf(w, v.y, s[nt][3]);
+                }
+            }
+        } else {
+            for (int g = 0; g < NH; ++g) {
+                const float w = tk[g];
+                const uint32_t sg = map_to_rank(s_base + (uint32_t)((((g % HPC) * MT_ROWS + r_lo) * SP + c_lo) * 4), (uint32_t)(g / HPC));
+#pragma unroll
+                for (int nt = 0; nt < BN / 8; ++nt) {
+                    const float2 u = ld_cluster_f2(sg + nt * 32);
+                    const float2 v = ld_cluster_f2(sg + (8 * SP + nt * 8) * 4);
+                    s[nt][0] = fmaf(w, u.x, s[nt][0]); s[nt][1] = fmaf(w, u.y, s[nt][1]);
+                    s[nt][2] = fmaf(w, v.x, s[nt][2]); s[nt][3] = fmaf(w, v.y, s[nt][3]);
+                }
+            }
+        }
+        // mask, online softmax (in powers of two)
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = j0 + nt * 8 + c_lo + (e & 1);
+                const bool seen = j <= p_row[e >> 1] && j >= lo_row[e >> 1];
+                s[nt][e] = seen ? s[nt][e] * MT_LOG2E : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+            }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
+            const float m_new = fmaxf(m_run[hh], mx[hh]);
+            m_use[hh] = m_new == -INFINITY ? 0.f : m_new;
+            alpha[hh] = fast_exp2(m_run[hh] - m_use[hh]);
+            m_run[hh] = m_new;
+            l_run[hh] *= alpha[hh];
+        }
+        if (alpha[0] != 1.f || alpha[1] != 1.f) {
+#pragma unroll
+            for (int i = 0; i < 2 * NDV; ++i) {
+                acc[i][0] *= alpha[0]; acc[i][1] *= alpha[0];
+                acc[i][2] *= alpha[1]; acc[i][3] *= alpha[1];
+            }
+        }
+        cp_async_wait<1>();                     // this tile's values (the next keys may still be on their way)
+        if (cl > 1) cluster_barrier(); else __syncthreads();       // and nobody reads this tile's scores any more
+#pragma unroll
+        for (int kp = 0; kp < BN / 16; ++kp) {
+            uint32_t pa[4];
+            float pv[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    pv[nt][e] = fast_exp2(s[2 * kp + nt][e] - m_use[e >> 1]);
+                    l_run[e >> 1] += pv[nt][e];
+                }
+            pa[0] = pack_bf16(pv[0][0], pv[0][1]);
+            pa[1] = pack_bf16(pv[0][2], pv[0][3]);
+            pa[2] = pack_bf16(pv[1][0], pv[1][1]);
+            pa[3] = pack_bf16(pv[1][2], pv[1][3]);
+#pragma unroll
+            for (int nd = 0; nd < NDV; ++nd) {
+                if (nd * 16 < DVP) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, vb + (kp * 16 + (mi & 1) * 8 + lr) * VP + (nd * 2 + (mi >> 1)) * 16);
+                    mma_bf16(acc[2 * nd], pa, b[0], b[1]);
+                    mma_bf16(acc[2 * nd + 1], pa, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();                        // the value buffer is free
+        if (t + 1 < n_t) load_values(t + 1);
+        cp_async_commit();
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int r = r_lo + hh * 8;
+        if (r >= rows) continue;
+        const float inv = l_run[hh] > 0.f ? 1.f / l_run[hh] : 0.f;
+        bf16* o = a.out + (size_t)(tok0 + r) * a.out_stride + (size_t)h * DV + c_lo;
+#pragma unroll
+        for (int i = 0; i < 2 * NDV; ++i)
+            if (i * 8 + c_lo < DV)
+                *reinterpret_cast<__nv_bfloat162*>(o + i * 8) = __floats2bfloat162_rn(acc[i][2 * hh] * inv, acc[i][2 * hh + 1] * inv);
+    }
+    if (cl > 1) cluster_barrier();              // a CTA's scores may be read by the others until their last mix is done
+}
+
+static int mixed_tc_cluster(int NH) {
+    for (int cl = 1; cl <= 4; cl *= 2)
+        if (NH % cl == 0 && NH / cl <= MT_MAX_WARPS) return cl;
+    return 0;
+}
+
+static size_t mixed_tc_smem(const MixedArgs& a, int BN) {
+    const int HPC = a.NH / a.cl, group = a.NH / a.NKV;
+    const int n_kv = HPC >= group ? HPC / group : 1;
+    const size_t QP = ((a.D + 15) & ~15) * 2 + 16, VP = ((a.DV + 15) & ~15) * 2 + 16;
+    return (size_t)HPC * MT_ROWS * QP + (size_t)n_kv * BN * (QP + VP) + (size_t)HPC * MT_ROWS * (BN + 8) * 4 +
+           (size_t)HPC * a.NH * 4 + (size_t)a.rel_rows * a.NH * 4;
+}
+
+template <int BN, int NDV>
+static int launch_mixed_tc(const MixedArgs& a, size_t smem, cudaStream_t stream) {
+    static AcvSmemConfig cfg;
+    if (int rc = acv_ensure_smem(cfg, attn_mixed_tc_kernel<BN, NDV>, (int)smem)) return rc;
+    const int units = a.n_tiles * MT_SUB + a.n_dec;
+    acv_launch_cluster(PDL_ATTN, dim3(a.cl), attn_mixed_tc_kernel<BN, NDV>, dim3(units * a.cl), dim3(a.NH / a.cl * 32), smem,
+                       stream, a);
+    return acv_launch_status();
+}
+
+#define MT_SMEM_LIMIT (200 * 1024)
+
+// 1 if acv_attention_mixed_tc runs these sizes, 0 if they belong to acv_attention_mixed
+ACV_API int acv_attention_mixed_tc_takes(int NH, int NKV, int D, int DV, int rel_rows) {
+    if (NH <= 0 || NKV <= 0 || NH % NKV || D <= 0 || DV <= 0 || D % 8 || DV % 8 || DV > 128 || D > 512) return 0;
+    MixedArgs a = {};
+    a.NH = NH; a.NKV = NKV; a.D = D; a.DV = DV; a.rel_rows = rel_rows;
+    a.cl = mixed_tc_cluster(NH);
+    if (!a.cl) return 0;
+    const int HPC = NH / a.cl, group = NH / NKV;
+    if (HPC % group && group % HPC) return 0;       // a CTA's heads read whole key/value heads, every CTA as many
+    return mixed_tc_smem(a, 16) <= MT_SMEM_LIMIT;
+}
+
+// Portions (tiles of 128 query tokens: tile_seq, tile_q0) and one-token requests (dec_tokens, dec_seqs) of a step in
+// one launch.  q rows of NH*D bfloat16 at q_stride, out rows of NH*DV; pages [NP][NKV][page][D] and [..][DV]; temp
+// float [NH]; rel float [rel_rows][NH]; bucket_of int [n_dist]; talk float [NH][NH]; each of the four may be null.
+ACV_API int acv_attention_mixed_tc(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                   const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles,
+                                   const int* dec_tokens, const int* dec_seqs, int n_dec, const int* cu_q,
+                                   const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH,
+                                   int NKV, int D, int DV, int page_size, int num_pages, float scale, int window,
+                                   const float* temp, float cap, const float* rel, int rel_rows, const int* bucket_of,
+                                   int n_dist, int last_row, const float* talk, cudaStream_t stream) {
+    if (n_tiles <= 0 && n_dec <= 0) return 0;
+    if (!acv_attention_mixed_tc_takes(NH, NKV, D, DV, rel ? rel_rows : 0)) return ACV_ERR_SIZE;
+    if (rel && (!bucket_of || n_dist < 0 || last_row < 0 || last_row >= rel_rows)) return ACV_ERR_SIZE;
+    if (((uintptr_t)q & 15) || ((size_t)q_stride * 2) % 16 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) ||
+        ((uintptr_t)out & 3) || (out_stride & 1))
+        return ACV_ERR_ALIGN;
+    MixedArgs a = {(const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages,
+                   tile_seq, tile_q0, n_tiles < 0 ? 0 : n_tiles, dec_tokens, dec_seqs, n_dec < 0 ? 0 : n_dec, cu_q, kv_len,
+                   block_table, bt_stride, bt_rows, NH, NKV, D, DV, page_size, num_pages, scale, window,
+                   temp, cap, rel, bucket_of, n_dist, last_row, rel ? rel_rows : 0, talk, mixed_tc_cluster(NH)};
+    const int ndv = (DV + 15) / 16;
+    // the widest key tile that fits; 64 keys only with few accumulators (registers)
+    int BN = 16;
+    if (mixed_tc_smem(a, 32) <= MT_SMEM_LIMIT) BN = 32;
+    if (ndv <= 4 && mixed_tc_smem(a, 64) <= MT_SMEM_LIMIT) BN = 64;
+    const size_t smem = mixed_tc_smem(a, BN);
+#define MT_CASE(B, N) if (BN == B && ndv <= N) return launch_mixed_tc<B, N>(a, smem, stream);
+    MT_CASE(64, 2) MT_CASE(64, 4)
+    MT_CASE(32, 2) MT_CASE(32, 4) MT_CASE(32, 8)
+    MT_CASE(16, 2) MT_CASE(16, 4) MT_CASE(16, 8)
+#undef MT_CASE
+    return ACV_ERR_SIZE;
+}

@@ -86,6 +86,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_gemm_simt_batched": [P, I, LL, P, I, LL, P, I, LL, I, I, I, I, I, I, P],
         "acv_attention_mixed": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P, F, P, P, I, I, P, I, P],
+        "acv_attention_mixed_tc_takes": [I, I, I, I, I],
+        "acv_attention_mixed_tc": [P, I, P, I, P, P, P, P, I, P, P, I, P, P, P, I, P, I, I, I, I, I, I, F, I, P, F, P, I, P, I, I, P, P],
         "acv_add_normed_rmsnorm": [P, P, I, P, F, P, F, P, I, I, I, P],
         "acv_cast_rows_f32": [P, I, P, I, I, I, I, P],
         "acv_activation": [P, P, LL, I, F, F, I, P],
@@ -1476,25 +1478,48 @@ def distance_buckets(rows: int, far: float) -> tuple[torch.Tensor, int]:
     return torch.tensor(out, dtype=torch.int32), last
 
 
+def attention_mixed_tc_takes(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+                             rel_rows: int = 0) -> bool:
+    """Whether the tensor-core kernel of the head-mixing attention runs these sizes (bfloat16; head sizes in multiples of
+    8, values up to 128; up to 64 heads that split evenly over a cluster's CTAs; everything of a tile in shared memory)."""
+    return dtype == torch.bfloat16 and bool(library().acv_attention_mixed_tc_takes(num_heads, num_kv_heads, head_dim,
+                                                                                    value_dim, rel_rows))
+
+
 def attention_mixed(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                     positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
                     table_rows: torch.Tensor | None = None, value_dim: int = 0, temp: torch.Tensor | None = None,
                     softcap: float = 0.0, rel: torch.Tensor | None = None, bucket_of: torch.Tensor | None = None,
-                    last_row: int = 0, talk: torch.Tensor | None = None) -> torch.Tensor:
+                    last_row: int = 0, talk: torch.Tensor | None = None, ctx=None, work: dict | None = None) -> torch.Tensor:
     """Paged causal attention whose scores pass through more steps before the softmax: times ``temp`` [heads], a soft
     cap, plus ``rel`` [rows, heads] by bucketed distance (``bucket_of`` int32 [distances], larger distances read
     ``last_row``), then mixed across heads by ``talk`` [heads, heads]; each step optional.  Everything after the
-    score's product is float32; temp, rel and talk are float32 tensors."""
+    score's product is float32; temp, rel and talk are float32 tensors.
+
+    With the step's context and attention work lists (``ctx``, ``work``) bfloat16 runs take the tensor-core kernel
+    (tiles of 16 query tokens with all heads, one launch for portions and one-token requests); float32 runs, and sizes
+    that kernel refuses, take the kernel with one block a token."""
     _need_cuda(q, out, k_pages)
     for t in (temp, rel, talk):
         if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
             raise KernelError("attention_mixed: temp, rel and talk are contiguous float32 tensors")
     n_dist = bucket_of.numel() if bucket_of is not None else 0
+    value_dim = int(value_dim) or head_dim
+    rel_rows = rel.shape[0] if rel is not None else 0
+    if ctx is not None and work is not None and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and \
+            attention_mixed_tc_takes(q.dtype, num_heads, num_kv_heads, head_dim, value_dim, rel_rows):
+        _check(library().acv_attention_mixed_tc(
+            _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(work["tile_seq"]), _p(work["tile_q0"]),
+            work["n_tiles"], _p(work["dec_tokens"]), _p(work["dec_seqs"]), work["n_dec"], _p(ctx.cu_q), _p(ctx.kv_len),
+            _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads, head_dim, value_dim,
+            k_pages.shape[2], k_pages.shape[0], float(scale), int(window), _p(temp), float(softcap), _p(rel), rel_rows,
+            _p(bucket_of), n_dist, int(last_row), _p(talk), _stream()), "attention_mixed_tc")
+        return out
     _check(library().acv_attention_mixed(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(positions), _p(seq_of_token),
         _p(block_table), block_table.stride(0), _p(table_rows), q.shape[0], num_heads, num_kv_heads, head_dim,
-        int(value_dim) or head_dim, k_pages.shape[2], k_pages.shape[0], float(scale), int(window), _p(temp), float(softcap),
+        value_dim, k_pages.shape[2], k_pages.shape[0], float(scale), int(window), _p(temp), float(softcap),
         _p(rel), _p(bucket_of), n_dist, int(last_row), _p(talk), dtype_code(q.dtype), _stream()), "attention_mixed")
     return out
 

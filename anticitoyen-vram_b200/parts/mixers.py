@@ -163,7 +163,7 @@ class Attention(Mixer):
             ops.attention_mixed(qkv, out, cache.k_pages, cache.v_pages, ctx.positions, ctx.seq_of_token, table, NH, NKV, D,
                                 self.scale, self.window, table_rows=ctx.table_rows, value_dim=DV, temp=self.temp,
                                 softcap=float(self.score.get("softcap", 0.0) or 0.0), rel=self.rel, bucket_of=self.bucket_of,
-                                last_row=self.rel_last, talk=self.talk)
+                                last_row=self.rel_last, talk=self.talk, ctx=ctx, work=ctx.work.get(self.metadata_key))
             return
         ops.attention(qkv, out, cache.k_pages, cache.v_pages, ctx, table, NH, NKV, D, self.scale, self.window,
                       work=ctx.work[self.metadata_key], value_dim=DV, keep_first=self.keep_first)

@@ -1,0 +1,134 @@
+"""The attention kernels of the Nizedra parts alone, on pages filled by hand, against dense float64 sums written out
+here: the head-mixing attention in both of its kernels (one block a token; tiles of 16 tokens with all heads on the
+tensor cores, a cluster of CTAs where the heads are many), portions beside one-token requests in one call, pages in
+any order, windows, bias tables whose last row is reached, keys at page borders."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+from acvram_b200.kernels import ops
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+class Step:
+    pass
+
+
+def paged_case(NKV, D, DV, page, lens, q_lens, seed, dtype):
+    """Pages in a shuffled order for requests of ``lens`` tokens whose last ``q_lens`` are this step's; unit-RMS keys."""
+    g = torch.Generator().manual_seed(seed)
+    per = [(n + page - 1) // page for n in lens]
+    n_pages = sum(per) + 3
+    order = torch.randperm(n_pages, generator=g)
+    table = torch.full((len(lens), max(per)), -1, dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(per):
+        table[b, :n] = order[at:at + n]
+        at += n
+    k = torch.randn(n_pages, NKV, page, D, generator=g)
+    k = (k / k.pow(2).mean(-1, keepdim=True).sqrt()).to(dtype)
+    v = torch.randn(n_pages, NKV, page, DV, generator=g).to(dtype)
+    ctx = Step()
+    ctx.positions = torch.cat([torch.arange(n - q, n) for n, q in zip(lens, q_lens)]).to(torch.int32).to(DEV)
+    ctx.seq_of_token = torch.cat([torch.full((q,), b) for b, q in enumerate(q_lens)]).to(torch.int32).to(DEV)
+    cu = [0]
+    for q in q_lens:
+        cu.append(cu[-1] + q)
+    ctx.cu_q = torch.tensor(cu, dtype=torch.int32, device=DEV)
+    ctx.kv_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    ctx.table_rows = None
+    arrays, values = ops.attention_work(q_lens, lens, cu)
+    work = {n: torch.as_tensor(a).to(DEV) for n, a in arrays.items()}
+    work.update(values)
+    return ctx, work, table.to(DEV), k.to(DEV), v.to(DEV), cu[-1]
+
+
+def dense_mixed(q, k_pages, v_pages, table, lens, q_lens, NH, NKV, D, DV, scale, window, temp, cap, rel, far, talk):
+    """float64, request by request: score, times temp, soft cap, plus the bias of the distance's row, mixed over the
+    heads, softmax over the visible keys, weighted sum of values."""
+    page = k_pages.shape[2]
+    out = []
+    t0 = 0
+    rows = rel.shape[0] if rel is not None else 0
+
+    def row_of(n):
+        half = rows // 2
+        return n if n < half else min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+
+    for b, (n, ql) in enumerate(zip(lens, q_lens)):
+        pages = table[b].long().cpu()
+        js = torch.arange(n)
+        kk = k_pages.cpu().double()[pages[js // page], :, js % page]          # [n, NKV, D]
+        vv = v_pages.cpu().double()[pages[js // page], :, js % page]
+        qq = q[t0:t0 + ql, :NH * D].cpu().double().view(ql, NH, D)
+        s = torch.einsum("ihd,jhd->hij", qq, kk.repeat_interleave(NH // NKV, dim=1)) * scale
+        if temp is not None:
+            s = s * temp.cpu().double()[:, None, None]
+        if cap > 0:
+            s = cap * torch.tanh(s / cap)
+        pos = torch.arange(n - ql, n)
+        dist = pos[:, None] - js[None, :]
+        if rel is not None:
+            idx = torch.tensor([[row_of(int(d)) if d >= 0 else 0 for d in r] for r in dist])
+            s = s + rel.cpu().double()[idx].permute(2, 0, 1)
+        if talk is not None:
+            s = torch.einsum("hg,gij->hij", talk.cpu().double(), s)
+        seen = (dist >= 0) & ((dist < window) if window > 0 else torch.ones_like(dist, dtype=torch.bool))
+        p = torch.softmax(s.masked_fill(~seen, -math.inf), dim=-1)
+        out.append(torch.einsum("hij,jhd->ihd", p, vv.repeat_interleave(NH // NKV, dim=1)).reshape(ql, NH * DV))
+        t0 += ql
+    return torch.cat(out)
+
+
+CASES = [
+    # NH NKV  D   DV page  lens             q_lens          window rel far   cap
+    (4, 2, 16, 24, 16, [37, 5, 70], [37, 1, 20], 0, 12, 100.0, 30.0),
+    (4, 2, 48, 48, 16, [150, 129, 64, 17], [150, 1, 2, 17], 0, 16, 120.0, 50.0),      # the last row is reached
+    (3, 3, 40, 8, 16, [100, 33], [50, 1], 20, 6, 17.0, 0.0),                          # a window, no cap, odd head count
+    (8, 1, 64, 64, 64, [200, 150], [130, 1], 48, 0, 0.0, 0.0),                        # no bias table
+    (32, 8, 32, 32, 16, [90, 60], [40, 1], 0, 8, 50.0, 20.0),                         # a cluster of two CTAs
+    (40, 40, 16, 16, 16, [50, 33], [18, 1], 0, 10, 40.0, 10.0),                       # a cluster of four
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: f"h{c[0]}k{c[1]}d{c[2]}v{c[3]}")
+def test_head_mixing_attention_kernels(case):
+    NH, NKV, D, DV, page, lens, q_lens, window, rel_rows, far, cap = case
+    ctx, work, table, k, v, T = paged_case(NKV, D, DV, page, lens, q_lens, 5 + NH, torch.bfloat16)
+    g = torch.Generator().manual_seed(NH * 7 + D)
+    q = torch.randn(T, NH * D + 64, generator=g)                 # queries are the first columns of wider rows
+    q = (q / q.pow(2).mean(-1, keepdim=True).sqrt()).to(torch.bfloat16).to(DEV)
+    temp = (torch.rand(NH, generator=g) + 0.5).to(DEV)
+    talk = (torch.eye(NH) + 0.2 * torch.randn(NH, NH, generator=g)).contiguous().to(DEV)
+    rel = torch.randn(rel_rows, NH, generator=g).to(DEV) if rel_rows else None
+    bucket, last = ops.distance_buckets(rel_rows, far) if rel_rows else (None, 0)
+    bucket = bucket.to(DEV) if bucket is not None else None
+    scale = D ** -0.5 * 6.0
+    want = dense_mixed(q, k, v, table, lens, q_lens, NH, NKV, D, DV, scale, window, temp, cap, rel, far, talk)
+    kw = dict(value_dim=DV, temp=temp, softcap=cap, rel=rel, bucket_of=bucket, last_row=last, talk=talk)
+    ref = float(want.abs().max())
+    # one block a token, in float32 on the same (bfloat16-exact) numbers
+    out = torch.zeros((T, NH * DV), device=DEV, dtype=torch.float32)
+    ops.attention_mixed(q.float(), out, k.float(), v.float(), ctx.positions, ctx.seq_of_token, table, NH, NKV, D, scale,
+                        window, **kw)
+    assert float((out.cpu().double() - want).abs().max()) < 2e-4 * ref
+    # tensor cores: bfloat16 weights of the softmax and a bfloat16 result
+    assert ops.attention_mixed_tc_takes(torch.bfloat16, NH, NKV, D, DV, rel_rows)
+    out = torch.full((T, NH * DV), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.attention_mixed(q, out, k, v, ctx.positions, ctx.seq_of_token, table, NH, NKV, D, scale, window, ctx=ctx,
+                        work=work, **kw)
+    assert float((out.cpu().double() - want).abs().max()) < 2e-2 * ref
+
+
+def test_head_mixing_tensor_core_kernel_refuses_what_it_cannot_hold():
+    assert not ops.attention_mixed_tc_takes(torch.float32, 4, 2, 16, 16, 8)
+    assert not ops.attention_mixed_tc_takes(torch.bfloat16, 4, 2, 12, 16, 8)        # rows that are no 16-byte pieces
+    assert not ops.attention_mixed_tc_takes(torch.bfloat16, 4, 2, 16, 256, 8)       # values too wide for the registers
+    assert not ops.attention_mixed_tc_takes(torch.bfloat16, 6, 4, 16, 16, 8)
