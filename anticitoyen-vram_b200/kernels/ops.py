@@ -93,6 +93,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_activation": [P, P, LL, I, F, F, I, P],
         "acv_rmsnorm_rows": [P, I, P, F, P, I, I, I, I, P],
         "acv_latent_prepare": [P, I, P, I, P, I, P, F, P, I, I, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P],
+        "acv_attention_latent_tc_takes": [I, I, I],
+        "acv_attention_latent_tc": [P, I, P, I, P, P, P, I, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, P],
         "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, P, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
         "acv_gemm_tc_bias": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P, P],
@@ -1599,6 +1601,36 @@ def latent_prepare(q: torch.Tensor, q_out: torch.Tensor, kv: torch.Tensor, weigh
         block_table.stride(0) if block_table is not None else 0, _p(table_rows), _p(pages),
         pages.shape[2] if pages is not None else 1, pages.shape[0] if pages is not None else 0, q.shape[0], num_heads, dim,
         rot_dim, rank, dtype_code(q.dtype), _stream()), "latent_prepare")
+
+
+def attention_latent_tc_takes(dtype: torch.dtype, num_heads: int, row: int, rank: int) -> bool:
+    """Whether the tensor-core kernel over kept latent rows runs these sizes (bfloat16; rows and latents in multiples of
+    8 elements, latents up to 512; a unit's queries and two key tiles in shared memory)."""
+    return dtype == torch.bfloat16 and bool(library().acv_attention_latent_tc_takes(num_heads, row, rank))
+
+
+def attention_latent(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, ctx, block_table: torch.Tensor,
+                     num_heads: int, row: int, rank: int, scale: float, window: int = 0,
+                     work: dict | None = None) -> torch.Tensor:
+    """Attention of every token of the step over its request's kept rows: ``q`` [T, heads*row] are the queries that meet
+    the rows of ``pages`` [num_pages, 1, page_size, row]; ``out`` [T, heads*rank] gets the weighted sums of the rows'
+    first ``rank`` elements.  Causal, with ``window`` > 0 limited to the last ``window`` rows.
+
+    With the step's attention work lists (``work``) bfloat16 runs take the tensor-core kernel (one launch for portions
+    and one-token requests; csrc/latent_attention_tc.cu); float32 runs, and sizes that kernel refuses, take the generic
+    paged kernel with the pages as keys and as values."""
+    _need_cuda(q, out, pages)
+    rows = getattr(ctx, "table_rows", None)
+    if work is not None and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and pages.is_contiguous() and \
+            attention_latent_tc_takes(q.dtype, num_heads, row, rank):
+        _check(library().acv_attention_latent_tc(
+            _p(q), q.stride(0), _p(out), out.stride(0), _p(pages), _p(work["tile_seq"]), _p(work["tile_q0"]),
+            work["n_tiles"], _p(work["dec_tokens"]), _p(work["dec_seqs"]), work["n_dec"], _p(ctx.cu_q), _p(ctx.kv_len),
+            _p(block_table), block_table.stride(0), _p(rows), num_heads, row, rank, pages.shape[2], pages.shape[0],
+            float(scale), int(window), _stream()), "attention_latent_tc")
+        return out
+    return attention_generic(q, out, pages, pages, ctx.positions, ctx.seq_of_token, block_table, num_heads, 1, row, scale,
+                             window, table_rows=rows, value_dim=rank)
 
 
 def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out: torch.Tensor) -> torch.Tensor:

@@ -481,6 +481,13 @@ class LatentAttention(Mixer):
     Tensors behind ``prefix``: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, o (``names`` renames them); no biases."""
 
     NAMES = {n: n for n in ("dq", "dq.norm", "uq", "dkv", "dkv.norm", "uk", "uv", "o")}
+    metadata_key = "attention"      # the work lists of the attention kernels serve this layer as well
+
+    def step_metadata(self, q_lens, kv_lens, cu_q) -> StepMetadata:
+        return StepMetadata(*ops.attention_work(q_lens, kv_lens, cu_q))
+
+    def decode_metadata(self, padded: int, max_kv: int) -> StepMetadata:
+        return StepMetadata(*ops.attention_work_decode(padded, max_kv))
 
     def __init__(self, hidden_size: int, num_heads: int, dim: int, rot_dim: int, value_dim: int, q_rank: int, kv_rank: int,
                  scale: float | None, norm_eps: float, position: PartSpec, window: int = 0, prefix: str = "mix.",
@@ -563,8 +570,8 @@ class LatentAttention(Mixer):
                            cache.k_pages if cache.writes else None, H, D, R, KR, table_rows=ctx.table_rows)
         ops.gemm_batched(q.view(T, H, D + R)[:, :, :D], self.uk_t, met.view(T, H, self.row)[:, :, :KR])
         lat = torch.empty((T, H * KR), device=h.device, dtype=h.dtype)            # weighted sums of latents
-        ops.attention_generic(met, lat, cache.k_pages, cache.k_pages, ctx.positions, ctx.seq_of_token, table, H, 1,
-                              self.row, self.scale, self.window, table_rows=ctx.table_rows, value_dim=KR)
+        ops.attention_latent(met, lat, cache.k_pages, ctx, table, H, self.row, KR, self.scale, self.window,
+                             work=ctx.work.get(self.metadata_key))
         out = torch.empty((T, H * DV), device=h.device, dtype=h.dtype)
         ops.gemm_batched(lat.view(T, H, KR), self.uv, out.view(T, H, DV))
         return self.o(out)

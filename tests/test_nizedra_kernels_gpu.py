@@ -1,7 +1,8 @@
 """The attention kernels of the Nizedra parts alone, on pages filled by hand, against dense float64 sums written out
 here: the head-mixing attention in both of its kernels (one block a token; tiles of 16 tokens with all heads on the
 tensor cores, a cluster of CTAs where the heads are many), portions beside one-token requests in one call, pages in
-any order, windows, bias tables whose last row is reached, keys at page borders."""
+any order, windows, bias tables whose last row is reached, keys at page borders; and the attention over kept latent
+rows (one key/value head whose values are the front of its keys) in its generic and its tensor-core kernel."""
 
 from __future__ import annotations
 
@@ -132,3 +133,58 @@ def test_head_mixing_tensor_core_kernel_refuses_what_it_cannot_hold():
     assert not ops.attention_mixed_tc_takes(torch.bfloat16, 4, 2, 12, 16, 8)        # rows that are no 16-byte pieces
     assert not ops.attention_mixed_tc_takes(torch.bfloat16, 4, 2, 16, 256, 8)       # values too wide for the registers
     assert not ops.attention_mixed_tc_takes(torch.bfloat16, 6, 4, 16, 16, 8)
+
+
+LATENT_CASES = [
+    # NH  ROW  KR  page  lens              q_lens        window
+    (8, 144, 128, 64, [200, 150, 97], [130, 1, 2], 96),          # one warp a row group; a portion, a decoded token, two tokens
+    (4, 40, 32, 16, [70, 33], [70, 1], 0),                       # narrow values, no window, rows that are no multiple of 16
+    (16, 320, 256, 16, [300, 140], [45, 1], 64),                 # two warps share a row group
+    (16, 576, 512, 64, [400, 300, 64], [150, 1, 1], 128),        # four warps share a row group; key tiles of 32
+    (3, 72, 48, 16, [90, 21], [17, 1], 10),                      # odd head count: a row group holds heads of several tokens
+    (80, 576, 512, 16, [60, 40], [9, 1], 0),                     # more heads than one CTA takes: head blocks
+]
+
+
+@pytest.mark.parametrize("case", LATENT_CASES, ids=lambda c: f"h{c[0]}row{c[1]}kr{c[2]}")
+def test_latent_rows_attention_kernels(case):
+    NH, ROW, KR, page, lens, q_lens, window = case
+    ctx, work, table, k, _, T = paged_case(1, ROW, 8, page, lens, q_lens, 11 + NH, torch.bfloat16)
+    v = k[..., :KR].contiguous()                                   # the values: the first KR elements of the kept rows
+    g = torch.Generator().manual_seed(NH * 5 + ROW)
+    q = torch.randn(T, NH * ROW, generator=g)
+    q = (q / q.pow(2).mean(-1, keepdim=True).sqrt()).to(torch.bfloat16).to(DEV)
+    scale = ROW ** -0.5 * 5.0
+    want = dense_mixed(q, k, v, table, lens, q_lens, NH, 1, ROW, KR, scale, window, None, 0.0, None, 0.0, None)
+    ref = float(want.abs().max())
+    # the generic paged kernel in float32 on the same (bfloat16-exact) numbers
+    out = torch.zeros((T, NH * KR), device=DEV, dtype=torch.float32)
+    ops.attention_latent(q.float(), out, k.float(), ctx, table, NH, ROW, KR, scale, window)
+    assert float((out.cpu().double() - want).abs().max()) < 2e-4 * ref
+    # tensor cores: bfloat16 weights of the softmax and a bfloat16 result
+    assert ops.attention_latent_tc_takes(torch.bfloat16, NH, ROW, KR)
+    before = ops.LAUNCHES
+    out = torch.full((T, NH * KR), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.attention_latent(q, out, k, ctx, table, NH, ROW, KR, scale, window, work=work)
+    assert ops.LAUNCHES == before + 1
+    assert float((out.cpu().double() - want).abs().max()) < 2e-2 * ref
+    # one-token requests alone take units of one token
+    dec = [i for i, n in enumerate(q_lens) if n == 1]
+    arrays, values = ops.attention_work([1] * len(dec), [lens[i] for i in dec], list(range(len(dec) + 1)))
+    work1 = {n: torch.as_tensor(a).to(DEV) for n, a in arrays.items()}
+    work1.update(values)
+    step = Step()
+    step.cu_q = torch.arange(len(dec) + 1, dtype=torch.int32, device=DEV)
+    step.kv_len = torch.tensor([lens[i] for i in dec], dtype=torch.int32, device=DEV)
+    step.table_rows = None
+    rows = torch.tensor([sum(q_lens[:i]) for i in dec], device=DEV)
+    out1 = torch.full((len(dec), NH * KR), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.attention_latent(q[rows].contiguous(), out1, k, step, table[torch.tensor(dec, device=DEV)].contiguous(), NH, ROW, KR,
+                         scale, window, work=work1)
+    assert float((out1.cpu().double() - want[rows.cpu()]).abs().max()) < 2e-2 * ref
+
+
+def test_latent_rows_tensor_core_kernel_refuses_what_it_cannot_hold():
+    assert not ops.attention_latent_tc_takes(torch.float32, 8, 144, 128)
+    assert not ops.attention_latent_tc_takes(torch.bfloat16, 8, 140, 128)           # rows that are no 16-byte pieces
+    assert not ops.attention_latent_tc_takes(torch.bfloat16, 8, 1088, 1024)         # latents too wide for the registers
