@@ -44,6 +44,13 @@ __device__ __forceinline__ float2 ld_cluster_f2(uint32_t addr) {
     return v;
 }
 
+// tanh(x) = 1 - 2 / (e^(2x) + 1) on the hardware's 2^x and reciprocal: absolute error about 2e-7 (the subtraction loses
+// nothing that matters where |x| is small: the result is then scaled by the cap, and the error stays absolute)
+__device__ __forceinline__ float fast_tanh(float x) {
+    const float e = fast_exp2(x * (2.f * MT_LOG2E));
+    return 1.f - __fdividef(2.f, e + 1.f);
+}
+
 struct MixedArgs {
     const bf16* q; int q_stride; bf16* out; int out_stride;
     const bf16* k_pages; const bf16* v_pages;
@@ -132,34 +139,35 @@ attn_mixed_tc_kernel(const MixedArgs a) {
     if (a.rel)
         for (int id = tid; id < a.rel_rows * NH; id += nthr) rel_s[id] = a.rel[id];
 
+    // a chunk's place: id = (kvl * BN + r) * CH + c, one division by CH (BN is a power of two); a key's page by a shift
+    // where the page size is a power of two
+    const int page_shift = (a.page_size & (a.page_size - 1)) == 0 ? __ffs(a.page_size) - 1 : -1;
+    auto row_of_key = [&](int j, int kvh, bool& ok) -> size_t {
+        const int pi = page_shift >= 0 ? j >> page_shift : j / a.page_size;
+        const int pg = bt[pi];
+        ok = pg >= 0 && pg < a.num_pages;
+        return ((size_t)pg * NKV + kvh) * a.page_size + (j - pi * a.page_size);
+    };
     auto load_keys = [&](int t) {
         const int j0 = j_first + t * BN;
         for (int id = tid; id < n_kv * BN * CH; id += nthr) {
-            const int c = id % CH, r = (id / CH) % BN, kvl = id / (CH * BN);
+            const int rr = id / CH, c = id - rr * CH, r = rr & (BN - 1), kvl = rr / BN;
             const int j = j0 + r;
             bool ok = j <= hi && j >= lo && c * 8 < D;
             size_t off = 0;
-            if (ok) {
-                const int pg = bt[j / a.page_size];
-                ok = pg >= 0 && pg < a.num_pages;
-                off = (((size_t)pg * NKV + kv_first + kvl) * a.page_size + (j % a.page_size)) * D + c * 8;
-            }
-            cp_async16(smem_u32(k_s + ((size_t)kvl * BN + r) * QP + c * 16), ok ? (const void*)(a.k_pages + off) : (const void*)a.k_pages, ok);
+            if (ok) off = row_of_key(j, kv_first + kvl, ok) * D + c * 8;
+            cp_async16(smem_u32(k_s + (size_t)rr * QP + c * 16), ok ? (const void*)(a.k_pages + off) : (const void*)a.k_pages, ok);
         }
     };
     auto load_values = [&](int t) {
         const int j0 = j_first + t * BN;
         for (int id = tid; id < n_kv * BN * CHV; id += nthr) {
-            const int c = id % CHV, r = (id / CHV) % BN, kvl = id / (CHV * BN);
+            const int rr = id / CHV, c = id - rr * CHV, r = rr & (BN - 1), kvl = rr / BN;
             const int j = j0 + r;
             bool ok = j <= hi && j >= lo && c * 8 < DV;
             size_t off = 0;
-            if (ok) {
-                const int pg = bt[j / a.page_size];
-                ok = pg >= 0 && pg < a.num_pages;
-                off = (((size_t)pg * NKV + kv_first + kvl) * a.page_size + (j % a.page_size)) * DV + c * 8;
-            }
-            cp_async16(smem_u32(v_s + ((size_t)kvl * BN + r) * VP + c * 16), ok ? (const void*)(a.v_pages + off) : (const void*)a.v_pages, ok);
+            if (ok) off = row_of_key(j, kv_first + kvl, ok) * DV + c * 8;
+            cp_async16(smem_u32(v_s + (size_t)rr * VP + c * 16), ok ? (const void*)(a.v_pages + off) : (const void*)a.v_pages, ok);
         }
     };
     load_keys(0);
@@ -212,7 +220,7 @@ attn_mixed_tc_kernel(const MixedArgs a) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float x = s[nt][e] * qk_scale;
-                if (cap > 0.f) x = cap * tanhf(x * inv_cap);
+                if (cap > 0.f) x = cap * fast_tanh(x * inv_cap);
                 if (a.rel) {
                     const int dist = p_row[e >> 1] - (j0 + nt * 8 + c_lo + (e & 1));
                     if (dist >= 0) x += rel_s[(dist < a.n_dist ? a.bucket_of[dist] : a.last_row) * NH + h];

@@ -350,8 +350,85 @@ def norm_shift_case(q_len: int, batch: int, reps: int, H: int = 4096) -> dict:
     print(line)
     return res
 
+# ----------------------------------------------------------------------------- attention with score steps; over kept latent rows
+class _Step:
+    pass
+
+
+def _paged_step(q_len: int, batch: int, context: int, page: int):
+    """The step's context, work lists and block table for ``batch`` requests that hold ``context`` tokens, the last
+    ``q_len`` of them new; pages in order."""
+    dev = "cuda"
+    per = (context + page - 1) // page
+    table = torch.arange(batch * per, device=dev, dtype=torch.int32).view(batch, per)
+    ctx = _Step()
+    ctx.positions = torch.arange(context - q_len, context, device=dev, dtype=torch.int32).repeat(batch)
+    ctx.seq_of_token = torch.arange(batch, device=dev, dtype=torch.int32).repeat_interleave(q_len)
+    cu = [i * q_len for i in range(batch + 1)]
+    ctx.cu_q = torch.tensor(cu, device=dev, dtype=torch.int32)
+    ctx.kv_len = torch.full((batch,), context, device=dev, dtype=torch.int32)
+    ctx.table_rows = None
+    arrays, values = ops.attention_work([q_len] * batch, [context] * batch, cu)
+    work = {**{k: torch.from_numpy(v).to(dev) for k, v in arrays.items()}, **values}
+    return ctx, work, table, batch * per
+
+
+def mixed_attention_case(q_len: int, batch: int, context: int, reps: int, NH: int = 16, NKV: int = 4, D: int = 128,
+                         page: int = 64, rel_rows: int = 32) -> dict:
+    """Head-mixing attention (a number per head, soft cap, distance bias, mix across heads) on the tensor cores."""
+    dev = "cuda"
+    ctx, work, table, n_pages = _paged_step(q_len, batch, context, page)
+    T = q_len * batch
+    q = torch.randn(T, NH * D, device=dev).to(torch.bfloat16)
+    k = torch.randn(n_pages, NKV, page, D, device=dev).to(torch.bfloat16)
+    v = torch.randn(n_pages, NKV, page, D, device=dev).to(torch.bfloat16)
+    temp = torch.rand(NH, device=dev) + 0.5
+    talk = (torch.eye(NH, device=dev) + 0.1 * torch.randn(NH, NH, device=dev)).contiguous()
+    rel = torch.randn(rel_rows, NH, device=dev)
+    bucket, last = ops.distance_buckets(rel_rows, 4096.0)
+    bucket = bucket.to(dev)
+    out = torch.empty(T, NH * D, device=dev, dtype=torch.bfloat16)
+    fn = lambda i: ops.attention_mixed(q, out, k, v, ctx.positions, ctx.seq_of_token, table, NH, NKV, D, D ** -0.5, 0,
+                                       temp=temp, softcap=50.0, rel=rel, bucket_of=bucket, last_row=last, talk=talk,
+                                       ctx=ctx, work=work)
+    us = _time(fn, reps)
+    seen = batch * (q_len * (context - q_len) + q_len * (q_len + 1) / 2)
+    flops = 4.0 * NH * D * seen
+    nbytes = batch * context * 2 * NKV * D * 2 + 2 * T * NH * D * 2
+    print(f"mixed attention q_len={q_len} batch={batch} context={context} heads={NH}/{NKV} of {D}: {us:.1f} us "
+          f"({flops / us / 1e6:.2f} TFLOP/s, {nbytes / us / 1e3:.0f} GB/s)")
+    return {"kernel": "attention_mixed_tc", "q_len": q_len, "batch": batch, "context": context, "us": us,
+            "tflops": flops / us / 1e6, "gbs": nbytes / us / 1e3}
+
+
+def latent_attention_case(q_len: int, batch: int, context: int, reps: int, NH: int = 16, ROW: int = 576, KR: int = 512,
+                          window: int = 1024, page: int = 64) -> dict:
+    """Attention over kept latent rows (one key/value head; values are the front of the keys) on the tensor cores."""
+    dev = "cuda"
+    ctx, work, table, n_pages = _paged_step(q_len, batch, context, page)
+    T = q_len * batch
+    q = torch.randn(T, NH * ROW, device=dev).to(torch.bfloat16)
+    pages = torch.randn(n_pages, 1, page, ROW, device=dev).to(torch.bfloat16)
+    out = torch.empty(T, NH * KR, device=dev, dtype=torch.bfloat16)
+    fn = lambda i: ops.attention_latent(q, out, pages, ctx, table, NH, ROW, KR, ROW ** -0.5, window, work=work)
+    us = _time(fn, reps)
+    seen = batch * sum(min(window, p + 1) if window > 0 else p + 1 for p in range(context - q_len, context))
+    flops = 2.0 * NH * (ROW + KR) * seen
+    keys = batch * (min(context, window + q_len - 1) if window > 0 else context)
+    nbytes = keys * ROW * 2 + T * NH * (ROW + KR) * 2
+    print(f"latent attention q_len={q_len} batch={batch} context={context} window={window} heads={NH} rows of {ROW} "
+          f"(values {KR}): {us:.1f} us ({flops / us / 1e6:.2f} TFLOP/s, {nbytes / us / 1e3:.0f} GB/s)")
+    return {"kernel": "attention_latent_tc", "q_len": q_len, "batch": batch, "context": context, "us": us,
+            "tflops": flops / us / 1e6, "gbs": nbytes / us / 1e3}
+
 
 CASES = {
+    "mixed_attention_prefill": lambda r: mixed_attention_case(2048, 1, 2048, r),
+    "mixed_attention_prefill_small": lambda r: mixed_attention_case(512, 1, 512, r),
+    "mixed_attention_decode_b64": lambda r: mixed_attention_case(1, 64, 2048, r),
+    "latent_attention_prefill": lambda r: latent_attention_case(2048, 1, 2048, r),
+    "latent_attention_prefill_small": lambda r: latent_attention_case(512, 1, 512, r, window=256),
+    "latent_attention_decode_b64": lambda r: latent_attention_case(1, 64, 2048, r),
     "retention_prefill": lambda r: retention_case(2048, 1, r),
     "retention_decode_b64": lambda r: retention_case(1, 64, r),
     "recurrence_prefill": lambda r: recurrence_case(2048, 1, r),
