@@ -88,6 +88,8 @@ attn_mixed_tc_kernel(const MixedArgs a) {
     float* s_s = reinterpret_cast<float*>(v_s + (size_t)n_kv_max * BN * VP);    // [HPC][16][SP]
     float* tk_s = s_s + (size_t)HPC * MT_ROWS * SP;                         // [HPC][NH]: rows of talk of this CTA's heads
     float* rel_s = tk_s + (size_t)HPC * NH;                                 // [rel_rows][NH]
+    float* bias_s = rel_s + (size_t)a.rel_rows * NH;                        // [HPC][BN + 16]: this tile's bias by distance
+    constexpr int NDD = BN + 16;
 
     pdl_launch_dependents();
     pdl_wait();
@@ -194,8 +196,18 @@ attn_mixed_tc_kernel(const MixedArgs a) {
         for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
+    if (a.rel) __syncthreads();                 // the bias table is in shared memory
     for (int t = 0; t < n_t; ++t) {
         const int j0 = j_first + t * BN;
+        if (a.rel) {
+            // the distances of this tile's (query, key) pairs span BN + 15 values from dmin on (row r, key c of the tile:
+            // dmin + r + BN - 1 - c): each head's bias for every one of them, looked up once
+            const int dmin = pos0 - (j0 + BN - 1);
+            for (int id = tid; id < HPC * NDD; id += nthr) {
+                const int w = id / NDD, dist = dmin + (id - w * NDD);
+                bias_s[id] = dist >= 0 ? rel_s[(dist < a.n_dist ? a.bucket_of[dist] : a.last_row) * NH + h_first + w] : 0.f;
+            }
+        }
         cp_async_wait<1>();                     // this tile's keys (its values may still be on their way)
         __syncthreads();
         float s[BN / 8][4];
@@ -221,10 +233,7 @@ attn_mixed_tc_kernel(const MixedArgs a) {
             for (int e = 0; e < 4; ++e) {
                 float x = s[nt][e] * qk_scale;
                 if (cap > 0.f) x = cap * fast_tanh(x * inv_cap);
-                if (a.rel) {
-                    const int dist = p_row[e >> 1] - (j0 + nt * 8 + c_lo + (e & 1));
-                    if (dist >= 0) x += rel_s[(dist < a.n_dist ? a.bucket_of[dist] : a.last_row) * NH + h];
-                }
+                if (a.rel) x += bias_s[warp * NDD + (r_lo + (e >> 1) * 8 + BN - 1) - (nt * 8 + c_lo + (e & 1))];
                 s[nt][e] = x;
             }
             *reinterpret_cast<float2*>(s_own + r_lo * SP + nt * 8 + c_lo) = make_float2(s[nt][0], s[nt][1]);
@@ -355,7 +364,7 @@ static size_t mixed_tc_smem(const MixedArgs& a, int BN) {
     const int n_kv = HPC >= group ? HPC / group : 1;
     const size_t QP = ((a.D + 15) & ~15) * 2 + 16, VP = ((a.DV + 15) & ~15) * 2 + 16;
     return (size_t)HPC * MT_ROWS * QP + (size_t)n_kv * BN * (QP + VP) + (size_t)HPC * MT_ROWS * (BN + 8) * 4 +
-           (size_t)HPC * a.NH * 4 + (size_t)a.rel_rows * a.NH * 4;
+           (size_t)HPC * a.NH * 4 + (size_t)a.rel_rows * a.NH * 4 + (size_t)HPC * (BN + 16) * 4;
 }
 
 template <int BN, int NDV>
