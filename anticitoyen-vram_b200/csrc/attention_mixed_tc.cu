@@ -63,6 +63,9 @@ struct MixedArgs {
     const float* temp; float cap; const float* rel; const int* bucket_of; int n_dist, last_row, rel_rows;
     const float* talk;
     int cl;                 // CTAs in a cluster (1, 2 or 4)
+    int n_split;            // CTAs (or clusters) that share the keys of a one-token request (1: none)
+    float* part_acc;        // n_split > 1: [n_dec][n_split][NH][DV] unnormalised sums
+    float* part_ml;         //              [n_dec][n_split][NH][2] running maximum (in powers of two) and sum
 };
 
 template <int BN, int NDV>
@@ -96,6 +99,7 @@ attn_mixed_tc_kernel(const MixedArgs a) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthr = blockDim.x;
     const int unit = blockIdx.x / cl;
     int seq, tok0, rows, pos0;
+    int split = 0, part = -1;                   // part >= 0: this CTA leaves a partial result at that index
     if (unit < a.n_tiles * MT_SUB) {
         const int tile = unit / MT_SUB;
         seq = a.tile_seq[tile];
@@ -106,7 +110,10 @@ attn_mixed_tc_kernel(const MixedArgs a) {
         rows = min(MT_ROWS, q_len - q0);
         pos0 = a.kv_len[seq] - q_len + q0;
     } else {
-        const int i = unit - a.n_tiles * MT_SUB;
+        const int u = unit - a.n_tiles * MT_SUB;
+        const int i = u / a.n_split;
+        split = u % a.n_split;
+        if (a.n_split > 1) part = u;
         seq = a.dec_seqs[i];
         tok0 = a.dec_tokens[i];
         rows = 1;
@@ -115,6 +122,13 @@ attn_mixed_tc_kernel(const MixedArgs a) {
     const int h = h_first + warp;
     const int kv_local = h / group - kv_first;
     if (pos0 < 0) {                              // a padded slot of a captured batch: nothing is kept for it
+        if (part >= 0) {
+            if (lane == 0) {
+                a.part_ml[((size_t)part * NH + h) * 2] = -INFINITY;
+                a.part_ml[((size_t)part * NH + h) * 2 + 1] = 0.f;
+            }
+            return;
+        }
         for (int e = lane; e < DV; e += 32) a.out[(size_t)tok0 * a.out_stride + (size_t)h * DV + e] = from_f32<bf16>(0.f);
         return;
     }
@@ -123,7 +137,11 @@ attn_mixed_tc_kernel(const MixedArgs a) {
     const int hi = pos0 + rows - 1;
     const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
     const int j_first = lo & ~(BN - 1);
-    const int n_t = (hi - j_first) / BN + 1;
+    const int n_all = (hi - j_first) / BN + 1;
+    // the tiles of this CTA: all of them, or its share of a one-token request's
+    const int per_split = (n_all + a.n_split - 1) / a.n_split;
+    const int t_first = part >= 0 ? split * per_split : 0;
+    const int n_t = part >= 0 ? min(n_all, t_first + per_split) : n_all;
     const int CH = DP / 8, CHV = DVP / 8;
 
     // queries of all local heads, the talk rows, the bias table
@@ -172,9 +190,9 @@ attn_mixed_tc_kernel(const MixedArgs a) {
             cp_async16(smem_u32(v_s + (size_t)rr * VP + c * 16), ok ? (const void*)(a.v_pages + off) : (const void*)a.v_pages, ok);
         }
     };
-    load_keys(0);
+    load_keys(t_first);
     cp_async_commit();
-    load_values(0);
+    load_values(t_first);
     cp_async_commit();
 
     const int mi = lane >> 3, lr = lane & 7;
@@ -197,7 +215,7 @@ attn_mixed_tc_kernel(const MixedArgs a) {
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     if (a.rel) __syncthreads();                 // the bias table is in shared memory
-    for (int t = 0; t < n_t; ++t) {
+    for (int t = t_first; t < n_t; ++t) {
         const int j0 = j_first + t * BN;
         if (a.rel) {
             // the distances of this tile's (query, key) pairs span BN + 15 values from dmin on (row r, key c of the tile:
@@ -339,6 +357,21 @@ attn_mixed_tc_kernel(const MixedArgs a) {
         l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
         l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
     }
+    if (part >= 0) {
+        // row 0 alone is a query: its unnormalised sums, running maximum and sum, for the merge
+        if (r_lo == 0) {
+            float* pa = a.part_acc + ((size_t)part * NH + h) * DV + c_lo;
+#pragma unroll
+            for (int i = 0; i < 2 * NDV; ++i)
+                if (i * 8 + c_lo < DV) *reinterpret_cast<float2*>(pa + i * 8) = make_float2(acc[i][0], acc[i][1]);
+            if (lane == 0) {
+                a.part_ml[((size_t)part * NH + h) * 2] = m_run[0];
+                a.part_ml[((size_t)part * NH + h) * 2 + 1] = l_run[0];
+            }
+        }
+        if (cl > 1) cluster_barrier();
+        return;
+    }
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         const int r = r_lo + hh * 8;
@@ -351,6 +384,31 @@ attn_mixed_tc_kernel(const MixedArgs a) {
                 *reinterpret_cast<__nv_bfloat162*>(o + i * 8) = __floats2bfloat162_rn(acc[i][2 * hh] * inv, acc[i][2 * hh + 1] * inv);
     }
     if (cl > 1) cluster_barrier();              // a CTA's scores may be read by the others until their last mix is done
+}
+
+// out[token][h] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) over the splits of a one-token request: a block a
+// (request, head), a thread a value column
+__global__ void attn_mixed_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                        const int* __restrict__ dec_tokens, bf16* __restrict__ out, int out_stride,
+                                        int n_split, int NH, int DV) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x / NH, h = blockIdx.x % NH;
+    float M = -INFINITY;
+    for (int s = 0; s < n_split; ++s) M = fmaxf(M, part_ml[(((size_t)i * n_split + s) * NH + h) * 2]);
+    for (int e = threadIdx.x; e < DV; e += blockDim.x) {
+        float sum = 0.f, L = 0.f;
+        if (M != -INFINITY)
+            for (int s = 0; s < n_split; ++s) {
+                const size_t at = ((size_t)i * n_split + s) * NH + h;
+                const float m = part_ml[at * 2];
+                if (m == -INFINITY) continue;
+                const float w = fast_exp2(m - M);
+                L = fmaf(part_ml[at * 2 + 1], w, L);
+                sum = fmaf(part_acc[at * DV + e], w, sum);
+            }
+        out[(size_t)dec_tokens[i] * out_stride + (size_t)h * DV + e] = from_f32<bf16>(L > 0.f ? sum / L : 0.f);
+    }
 }
 
 static int mixed_tc_cluster(int NH) {
@@ -371,9 +429,13 @@ template <int BN, int NDV>
 static int launch_mixed_tc(const MixedArgs& a, size_t smem, cudaStream_t stream) {
     static AcvSmemConfig cfg;
     if (int rc = acv_ensure_smem(cfg, attn_mixed_tc_kernel<BN, NDV>, (int)smem)) return rc;
-    const int units = a.n_tiles * MT_SUB + a.n_dec;
+    const int units = a.n_tiles * MT_SUB + a.n_dec * a.n_split;
     acv_launch_cluster(PDL_ATTN, dim3(a.cl), attn_mixed_tc_kernel<BN, NDV>, dim3(units * a.cl), dim3(a.NH / a.cl * 32), smem,
                        stream, a);
+    if (a.n_split > 1 && a.n_dec > 0)
+        acv_launch(PDL_ATTN, attn_mixed_merge_kernel, dim3(a.n_dec * a.NH), dim3(a.DV < 32 ? 32 : (a.DV + 31) / 32 * 32), 0,
+                   stream, (const float*)a.part_acc, (const float*)a.part_ml, a.dec_tokens, a.out, a.out_stride, a.n_split,
+                   a.NH, a.DV);
     return acv_launch_status();
 }
 
@@ -394,14 +456,18 @@ ACV_API int acv_attention_mixed_tc_takes(int NH, int NKV, int D, int DV, int rel
 // Portions (tiles of 128 query tokens: tile_seq, tile_q0) and one-token requests (dec_tokens, dec_seqs) of a step in
 // one launch.  q rows of NH*D bfloat16 at q_stride, out rows of NH*DV; pages [NP][NKV][page][D] and [..][DV]; temp
 // float [NH]; rel float [rel_rows][NH]; bucket_of int [n_dist]; talk float [NH][NH]; each of the four may be null.
+// n_split > 1: that many CTAs (or clusters) share the keys of every one-token request and leave partial results in
+// part_acc (float [n_dec][n_split][NH][DV]) and part_ml ([..][NH][2]), which a second launch merges into out.
 ACV_API int acv_attention_mixed_tc(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                    const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles,
                                    const int* dec_tokens, const int* dec_seqs, int n_dec, const int* cu_q,
                                    const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH,
                                    int NKV, int D, int DV, int page_size, int num_pages, float scale, int window,
                                    const float* temp, float cap, const float* rel, int rel_rows, const int* bucket_of,
-                                   int n_dist, int last_row, const float* talk, cudaStream_t stream) {
+                                   int n_dist, int last_row, const float* talk, int n_split, float* part_acc,
+                                   float* part_ml, cudaStream_t stream) {
     if (n_tiles <= 0 && n_dec <= 0) return 0;
+    if (n_split < 1 || (n_split > 1 && (!part_acc || !part_ml))) return ACV_ERR_SIZE;
     if (!acv_attention_mixed_tc_takes(NH, NKV, D, DV, rel ? rel_rows : 0)) return ACV_ERR_SIZE;
     if (rel && (!bucket_of || n_dist < 0 || last_row < 0 || last_row >= rel_rows)) return ACV_ERR_SIZE;
     if (((uintptr_t)q & 15) || ((size_t)q_stride * 2) % 16 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) ||
@@ -410,7 +476,8 @@ ACV_API int acv_attention_mixed_tc(const void* q, int q_stride, void* out, int o
     MixedArgs a = {(const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages,
                    tile_seq, tile_q0, n_tiles < 0 ? 0 : n_tiles, dec_tokens, dec_seqs, n_dec < 0 ? 0 : n_dec, cu_q, kv_len,
                    block_table, bt_stride, bt_rows, NH, NKV, D, DV, page_size, num_pages, scale, window,
-                   temp, cap, rel, bucket_of, n_dist, last_row, rel ? rel_rows : 0, talk, mixed_tc_cluster(NH)};
+                   temp, cap, rel, bucket_of, n_dist, last_row, rel ? rel_rows : 0, talk, mixed_tc_cluster(NH), n_split,
+                   part_acc, part_ml};
     const int ndv = (DV + 15) / 16;
     // the widest key tile that fits; 64 keys only with few accumulators (registers)
     int BN = 16;

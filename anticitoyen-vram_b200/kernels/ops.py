@@ -87,7 +87,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_gemm_simt_batched": [P, I, LL, P, I, LL, P, I, LL, I, I, I, I, I, I, P],
         "acv_attention_mixed": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P, F, P, P, I, I, P, I, P],
         "acv_attention_mixed_tc_takes": [I, I, I, I, I],
-        "acv_attention_mixed_tc": [P, I, P, I, P, P, P, P, I, P, P, I, P, P, P, I, P, I, I, I, I, I, I, F, I, P, F, P, I, P, I, I, P, P],
+        "acv_attention_mixed_tc": [P, I, P, I, P, P, P, P, I, P, P, I, P, P, P, I, P, I, I, I, I, I, I, F, I, P, F, P, I, P, I, I, P, I, P, P, P],
         "acv_add_normed_rmsnorm": [P, P, I, P, F, P, F, P, I, I, I, P],
         "acv_cast_rows_f32": [P, I, P, I, I, I, I, P],
         "acv_activation": [P, P, LL, I, F, F, I, P],
@@ -1480,6 +1480,9 @@ def distance_buckets(rows: int, far: float) -> tuple[torch.Tensor, int]:
     return torch.tensor(out, dtype=torch.int32), last
 
 
+MIXED_SPLIT_KEYS = 256      # no share of a one-token request's keys is shorter than this
+
+
 def attention_mixed_tc_takes(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
                              rel_rows: int = 0) -> bool:
     """Whether the tensor-core kernel of the head-mixing attention runs these sizes (bfloat16; head sizes in multiples of
@@ -1511,12 +1514,24 @@ def attention_mixed(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v
     rel_rows = rel.shape[0] if rel is not None else 0
     if ctx is not None and work is not None and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and \
             attention_mixed_tc_takes(q.dtype, num_heads, num_kv_heads, head_dim, value_dim, rel_rows):
+        # one-token requests: a CTA (or cluster) a request leaves most SMs idle and walks a long context alone, so the
+        # keys are shared among several (each at least MIXED_SPLIT_KEYS), as many as bring the launch to about the
+        # device's SMs; the partial results meet in a second small launch
+        n_dec, n_split, acc, ml = work["n_dec"], 1, None, None
+        if n_dec:
+            seen = min(work["max_dec_kv"], window) if window > 0 else work["max_dec_kv"]
+            clusters = 1 if num_heads <= 16 else (2 if num_heads <= 32 else 4)
+            room = max(1, sm_count(q.device) // (clusters * (n_dec + 8 * work["n_tiles"])))
+            n_split = max(1, min(room, seen // MIXED_SPLIT_KEYS, 16))
+            if n_split > 1:
+                parts = n_dec * n_split * num_heads
+                acc, ml, _ = _decode_scratch(q.device, parts * value_dim, parts * 2, 0)
         _check(library().acv_attention_mixed_tc(
             _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(work["tile_seq"]), _p(work["tile_q0"]),
             work["n_tiles"], _p(work["dec_tokens"]), _p(work["dec_seqs"]), work["n_dec"], _p(ctx.cu_q), _p(ctx.kv_len),
             _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads, head_dim, value_dim,
             k_pages.shape[2], k_pages.shape[0], float(scale), int(window), _p(temp), float(softcap), _p(rel), rel_rows,
-            _p(bucket_of), n_dist, int(last_row), _p(talk), _stream()), "attention_mixed_tc")
+            _p(bucket_of), n_dist, int(last_row), _p(talk), n_split, _p(acc), _p(ml), _stream()), "attention_mixed_tc")
         return out
     _check(library().acv_attention_mixed(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(positions), _p(seq_of_token),

@@ -96,6 +96,12 @@ CASES = [
     (8, 1, 64, 64, 64, [200, 150], [130, 1], 48, 0, 0.0, 0.0),                        # no bias table
     (32, 8, 32, 32, 16, [90, 60], [40, 1], 0, 8, 50.0, 20.0),                         # a cluster of two CTAs
     (40, 40, 16, 16, 16, [50, 33], [18, 1], 0, 10, 40.0, 10.0),                       # a cluster of four
+    # one-token requests whose keys several CTAs share (partial results merged by a second launch): alone, beside a
+    # portion, with a short request whose last shares are empty, under a window, in clusters
+    (4, 2, 32, 32, 16, [700, 520, 40], [1, 1, 1], 0, 12, 300.0, 30.0),
+    (8, 2, 64, 64, 64, [600, 900], [40, 1], 0, 16, 500.0, 50.0),
+    (4, 4, 16, 24, 16, [1500, 70], [1, 1], 600, 8, 90.0, 0.0),
+    (32, 8, 32, 32, 16, [800, 300], [1, 1], 0, 8, 50.0, 20.0),
 ]
 
 

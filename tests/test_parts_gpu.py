@@ -110,10 +110,10 @@ def test_kernels_refuse_cpu_tensors_and_unknown_types():
     with pytest.raises(KernelError):
         ops.swiglu(torch.zeros(2, 8, device="cuda", dtype=torch.float16), torch.zeros(2, 4, device="cuda", dtype=torch.float16))
     with pytest.raises(KernelError):   # head size beyond what the generic attention kernel takes
-        q = torch.zeros(1, 3 * 512, device="cuda")
-        pages = torch.zeros(1, 1, 16, 512, device="cuda")
+        q = torch.zeros(1, 3 * 2048, device="cuda")
+        pages = torch.zeros(1, 1, 16, 2048, device="cuda")
         z = torch.zeros(1, dtype=torch.int32, device="cuda")
-        ops.attention_generic(q, torch.zeros(1, 512, device="cuda"), pages, pages, z, z, z.view(1, 1), 1, 1, 512, 1.0)
+        ops.attention_generic(q, torch.zeros(1, 2048, device="cuda"), pages, pages, z, z, z.view(1, 1), 1, 1, 2048, 1.0)
 
 
 @pytest.mark.parametrize("name,dtype,window", [("A", "float32", 16), ("F", "bfloat16", 40), ("D", "bfloat16", 24)])
