@@ -122,7 +122,7 @@ def cmd_replay(args) -> int:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(prog="acvram", description="acvram_b200 - inference on one B200 (Qwen3 dense, Zotonex, Redudra)")
+    p = argparse.ArgumentParser(prog="acvram", description="acvram_b200 - inference on one B200 (Qwen3 dense, Zotonex, Redudra, Nizedra)")
     p.add_argument("--version", action="version", version=f"acvram_b200 {__version__}")
     sub = p.add_subparsers(dest="command", required=True)
 
