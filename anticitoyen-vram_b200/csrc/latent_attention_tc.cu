@@ -34,6 +34,9 @@ struct LatentArgs {
     int TOK;                // query tokens of a unit (divides 16)
     int HPC, HB;            // heads of a CTA, head blocks (HPC * HB == NH)
     int RG;                 // row groups of a CTA = ceil(TOK * HPC / 16)
+    int n_split;            // CTAs that share the rows of a one-token request (1: none)
+    float* part_acc;        // n_split > 1: [n_dec][n_split][NH][KR] unnormalised sums
+    float* part_ml;         //              [n_dec][n_split][NH][2] running maximum (in powers of two) and sum
 };
 
 template <int BN, int S, int NDV>
@@ -61,6 +64,7 @@ attn_latent_tc_kernel(const LatentArgs a) {
     const int hb = blockIdx.x % a.HB, unit = blockIdx.x / a.HB;
     const int per_tile = LT_TILE_TOKENS / a.TOK;
     int seq, tok0, ntok, pos0;
+    int split = 0, part = -1;                    // part >= 0: this CTA leaves a partial result at that index
     if (unit < a.n_tiles * per_tile) {
         const int tile = unit / per_tile;
         seq = a.tile_seq[tile];
@@ -71,7 +75,10 @@ attn_latent_tc_kernel(const LatentArgs a) {
         ntok = min(a.TOK, q_len - q0);
         pos0 = a.kv_len[seq] - q_len + q0;
     } else {
-        const int i = unit - a.n_tiles * per_tile;
+        const int u = unit - a.n_tiles * per_tile;
+        const int i = u / a.n_split;
+        split = u % a.n_split;
+        if (a.n_split > 1) part = u;
         seq = a.dec_seqs[i];
         tok0 = a.dec_tokens[i];
         ntok = 1;
@@ -80,6 +87,13 @@ attn_latent_tc_kernel(const LatentArgs a) {
     const int h_first = hb * HPC;
     const int n_rows = ntok * HPC;
     if (pos0 < 0) {                              // a padded slot of a captured batch: nothing is kept for it
+        if (part >= 0) {
+            for (int e = tid; e < HPC; e += nthr) {
+                a.part_ml[((size_t)part * a.NH + h_first + e) * 2] = -INFINITY;
+                a.part_ml[((size_t)part * a.NH + h_first + e) * 2 + 1] = 0.f;
+            }
+            return;
+        }
         for (int e = tid; e < HPC * KR; e += nthr)
             a.out[(size_t)tok0 * a.out_stride + (size_t)h_first * KR + e] = from_f32<bf16>(0.f);
         return;
@@ -89,7 +103,11 @@ attn_latent_tc_kernel(const LatentArgs a) {
     const int hi = pos0 + ntok - 1;
     const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
     const int j_first = lo & ~(BN - 1);
-    const int n_t = (hi - j_first) / BN + 1;
+    const int n_all = (hi - j_first) / BN + 1;
+    // the tiles of this CTA: all of them, or its share of a one-token request's
+    const int per_split = (n_all + a.n_split - 1) / a.n_split;
+    const int t_first = part >= 0 ? split * per_split : 0;
+    const int n_t = part >= 0 ? min(n_all, t_first + per_split) : n_all;
     const int CH = DP / 8;
 
     for (int id = tid; id < RG * 16 * CH; id += nthr) {
@@ -116,7 +134,7 @@ attn_latent_tc_kernel(const LatentArgs a) {
             cp_async16(smem_u32(dst + (size_t)r * QP + c * 16), ok ? (const void*)(a.pages + off) : (const void*)a.pages, ok);
         }
     };
-    load_keys(0);
+    load_keys(t_first);
     cp_async_commit();
 
     const int mi = lane >> 3, lr = lane & 7;
@@ -137,7 +155,7 @@ attn_latent_tc_kernel(const LatentArgs a) {
         for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-    for (int t = 0; t < n_t; ++t) {
+    for (int t = t_first; t < n_t; ++t) {
         const int j0 = j_first + t * BN;
         cp_async_wait<0>();
         __syncthreads();                                            // A
@@ -260,6 +278,25 @@ attn_latent_tc_kernel(const LatentArgs a) {
             l_run[1] += l_own[w * 16 + r_lo + 8];
         }
     }
+    if (part >= 0) {
+        // one token: row R is head h_first + R; unnormalised sums, running maximum and sum, for the merge
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int R = rg * 16 + r_lo + hh * 8;
+            if (R >= n_rows) continue;
+            const size_t at = (size_t)part * a.NH + h_first + R;
+            float* pa = a.part_acc + at * KR + sl * NDV * 16 + c_lo;
+#pragma unroll
+            for (int i = 0; i < 2 * NDV; ++i)
+                if (sl * NDV * 16 + i * 8 + c_lo < KR)
+                    *reinterpret_cast<float2*>(pa + i * 8) = make_float2(acc[i][2 * hh], acc[i][2 * hh + 1]);
+            if (sl == 0 && (lane & 3) == 0) {
+                a.part_ml[at * 2] = m_run[hh];
+                a.part_ml[at * 2 + 1] = l_run[hh];
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
         const int R = rg * 16 + r_lo + hh * 8;
@@ -270,6 +307,31 @@ attn_latent_tc_kernel(const LatentArgs a) {
         for (int i = 0; i < 2 * NDV; ++i)
             if (sl * NDV * 16 + i * 8 + c_lo < KR)
                 *reinterpret_cast<__nv_bfloat162*>(o + i * 8) = __floats2bfloat162_rn(acc[i][2 * hh] * inv, acc[i][2 * hh + 1] * inv);
+    }
+}
+
+// out[token][h] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) over the CTAs that shared a one-token request's rows:
+// a block a (request, head), a thread a few columns
+__global__ void attn_latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                         const int* __restrict__ dec_tokens, bf16* __restrict__ out, int out_stride,
+                                         int n_split, int NH, int KR) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x / NH, h = blockIdx.x % NH;
+    float M = -INFINITY;
+    for (int s = 0; s < n_split; ++s) M = fmaxf(M, part_ml[(((size_t)i * n_split + s) * NH + h) * 2]);
+    for (int e = threadIdx.x; e < KR; e += blockDim.x) {
+        float sum = 0.f, L = 0.f;
+        if (M != -INFINITY)
+            for (int s = 0; s < n_split; ++s) {
+                const size_t at = ((size_t)i * n_split + s) * NH + h;
+                const float m = part_ml[at * 2];
+                if (m == -INFINITY) continue;
+                const float w = fast_exp2(m - M);
+                L = fmaf(part_ml[at * 2 + 1], w, L);
+                sum = fmaf(part_acc[at * KR + e], w, sum);
+            }
+        out[(size_t)dec_tokens[i] * out_stride + (size_t)h * KR + e] = from_f32<bf16>(L > 0.f ? sum / L : 0.f);
     }
 }
 
@@ -314,8 +376,11 @@ template <int BN, int S, int NDV>
 static int launch_latent_tc(const LatentArgs& a, const LatentShape& sh, cudaStream_t stream) {
     static AcvSmemConfig cfg;
     if (int rc = acv_ensure_smem(cfg, attn_latent_tc_kernel<BN, S, NDV>, (int)sh.smem)) return rc;
-    const int units = a.n_tiles * (LT_TILE_TOKENS / a.TOK) + a.n_dec;
+    const int units = a.n_tiles * (LT_TILE_TOKENS / a.TOK) + a.n_dec * a.n_split;
     acv_launch(PDL_ATTN, attn_latent_tc_kernel<BN, S, NDV>, dim3(units * a.HB), dim3(a.RG * S * 32), sh.smem, stream, a);
+    if (a.n_split > 1 && a.n_dec > 0)
+        acv_launch(PDL_ATTN, attn_latent_merge_kernel, dim3(a.n_dec * a.NH), dim3(128), 0, stream, (const float*)a.part_acc,
+                   (const float*)a.part_ml, a.dec_tokens, a.out, a.out_stride, a.n_split, a.NH, a.KR);
     return acv_launch_status();
 }
 
@@ -327,12 +392,15 @@ ACV_API int acv_attention_latent_tc_takes(int NH, int ROW, int KR) {
 
 // Portions (tiles of 128 query tokens: tile_seq, tile_q0) and one-token requests (dec_tokens, dec_seqs) of a step in one
 // launch.  q rows of NH*ROW bfloat16 at q_stride (the queries that meet the kept rows), out rows of NH*KR (the weighted
-// sums of latents); pages [NP][1][page][ROW].
+// sums of latents); pages [NP][1][page][ROW].  n_split > 1: that many CTAs share the rows of every one-token request and
+// leave partial results in part_acc (float [n_dec][n_split][NH][KR]) and part_ml ([..][NH][2]); a second launch merges.
 ACV_API int acv_attention_latent_tc(const void* q, int q_stride, void* out, int out_stride, const void* pages,
                                     const int* tile_seq, const int* tile_q0, int n_tiles, const int* dec_tokens,
                                     const int* dec_seqs, int n_dec, const int* cu_q, const int* kv_len,
                                     const int* block_table, int bt_stride, const int* bt_rows, int NH, int ROW, int KR,
-                                    int page_size, int num_pages, float scale, int window, cudaStream_t stream) {
+                                    int page_size, int num_pages, float scale, int window, int n_split, float* part_acc,
+                                    float* part_ml, cudaStream_t stream) {
+    if (n_split < 1 || (n_split > 1 && (!part_acc || !part_ml))) return ACV_ERR_SIZE;
     if (n_tiles < 0) n_tiles = 0;
     if (n_dec < 0) n_dec = 0;
     if (n_tiles == 0 && n_dec == 0) return 0;
@@ -342,7 +410,7 @@ ACV_API int acv_attention_latent_tc(const void* q, int q_stride, void* out, int 
         return ACV_ERR_ALIGN;
     LatentArgs a = {(const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)pages, tile_seq, tile_q0, n_tiles,
                     dec_tokens, dec_seqs, n_dec, cu_q, kv_len, block_table, bt_stride, bt_rows, NH, ROW, KR, page_size,
-                    num_pages, scale, window, sh.TOK, sh.HPC, sh.HB, sh.RG};
+                    num_pages, scale, window, sh.TOK, sh.HPC, sh.HB, sh.RG, n_split, part_acc, part_ml};
 #define LT_CASE(B, SS, N) if (sh.BN == B && sh.S == SS && sh.NDV == N) return launch_latent_tc<B, SS, N>(a, sh, stream);
     LT_CASE(64, 1, 4) LT_CASE(64, 1, 8) LT_CASE(64, 2, 8) LT_CASE(64, 4, 8)
     LT_CASE(32, 1, 4) LT_CASE(32, 1, 8) LT_CASE(32, 2, 8) LT_CASE(32, 4, 8)

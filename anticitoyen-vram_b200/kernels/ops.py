@@ -94,7 +94,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_rmsnorm_rows": [P, I, P, F, P, I, I, I, I, P],
         "acv_latent_prepare": [P, I, P, I, P, I, P, F, P, I, I, P, P, P, I, P, P, I, I, I, I, I, I, I, I, P],
         "acv_attention_latent_tc_takes": [I, I, I],
-        "acv_attention_latent_tc": [P, I, P, I, P, P, P, I, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, P],
+        "acv_attention_latent_tc": [P, I, P, I, P, P, P, I, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, P, P, P],
         "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, P, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
         "acv_gemm_tc_bias": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P, P],
@@ -1638,11 +1638,21 @@ def attention_latent(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, ct
     rows = getattr(ctx, "table_rows", None)
     if work is not None and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and pages.is_contiguous() and \
             attention_latent_tc_takes(q.dtype, num_heads, row, rank):
+        # a step of one-token requests alone: a CTA a request leaves SMs idle, so the rows of a request are shared among
+        # several (each at least MIXED_SPLIT_KEYS), and a second small launch merges their partial results
+        n_dec, n_split, acc, ml = work["n_dec"], 1, None, None
+        if n_dec and not work["n_tiles"]:
+            seen = min(work["max_dec_kv"], window) if window > 0 else work["max_dec_kv"]
+            room = max(1, sm_count(q.device) // (n_dec * ((num_heads + 63) // 64)))
+            n_split = max(1, min(room, seen // MIXED_SPLIT_KEYS, 16))
+            if n_split > 1:
+                parts = n_dec * n_split * num_heads
+                acc, ml, _ = _decode_scratch(q.device, parts * rank, parts * 2, 0)
         _check(library().acv_attention_latent_tc(
             _p(q), q.stride(0), _p(out), out.stride(0), _p(pages), _p(work["tile_seq"]), _p(work["tile_q0"]),
             work["n_tiles"], _p(work["dec_tokens"]), _p(work["dec_seqs"]), work["n_dec"], _p(ctx.cu_q), _p(ctx.kv_len),
             _p(block_table), block_table.stride(0), _p(rows), num_heads, row, rank, pages.shape[2], pages.shape[0],
-            float(scale), int(window), _stream()), "attention_latent_tc")
+            float(scale), int(window), n_split, _p(acc), _p(ml), _stream()), "attention_latent_tc")
         return out
     return attention_generic(q, out, pages, pages, ctx.positions, ctx.seq_of_token, block_table, num_heads, 1, row, scale,
                              window, table_rows=rows, value_dim=rank)

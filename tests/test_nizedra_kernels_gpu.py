@@ -149,6 +149,8 @@ LATENT_CASES = [
     (16, 576, 512, 64, [400, 300, 64], [150, 1, 1], 128),        # four warps share a row group; key tiles of 32
     (3, 72, 48, 16, [90, 21], [17, 1], 10),                      # odd head count: a row group holds heads of several tokens
     (80, 576, 512, 16, [60, 40], [9, 1], 0),                     # more heads than one CTA takes: head blocks
+    (16, 144, 128, 16, [900, 40, 1300], [1, 1, 1], 0),           # one-token requests whose rows several CTAs share
+    (8, 320, 256, 64, [1500, 700], [1, 1], 600),                 # the same under a window
 ]
 
 
