@@ -85,6 +85,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_retention_gate": [P, I, P, I, P, I, I, I, I, F, F, I, P, I, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_gemm_simt_batched": [P, I, LL, P, I, LL, P, I, LL, I, I, I, I, I, I, P],
+        "acv_gemm_mma_batched_takes": [P, I, LL, P, I, LL, P, I, LL, I, I],
+        "acv_gemm_mma_batched": [P, I, LL, P, I, LL, P, I, LL, I, I, I, I, P],
         "acv_attention_mixed": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P, F, P, P, I, I, P, I, P],
         "acv_attention_mixed_tc_takes": [I, I, I, I, I],
         "acv_attention_mixed_tc": [P, I, P, I, P, P, P, P, I, P, P, I, P, P, P, I, P, I, I, I, I, I, I, F, I, P, F, P, I, P, I, I, P, I, P, P, P],
@@ -1586,13 +1588,20 @@ def activation(x: torch.Tensor, out: torch.Tensor, kind: str, p0: float = 0.0, p
 # ----------------------------------------------------------------------------- attention through a kept latent
 def gemm_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[:, b, :] = a[:, b, :] @ w[b]^T for every b: a [M, B, K] and out [M, B, N] are views with dense last
-    dimension (any row and batch strides), w [B, N, K] contiguous; 32-bit accumulation on the CUDA cores."""
+    dimension (any row and batch strides), w [B, N, K] contiguous; 32-bit accumulation.  bfloat16 views made of 16-byte
+    pieces run on the tensor cores (csrc/gemm_mma_batched.cu), everything else on the CUDA cores."""
     _need_cuda(a, w, out)
     M, B, K = a.shape
     N = w.shape[1]
     if w.shape != (B, N, K) or out.shape != (M, B, N) or a.stride(2) != 1 or out.stride(2) != 1 or not w.is_contiguous() \
             or a.dtype != w.dtype:
         raise KernelError(f"gemm_batched: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    lib = library()
+    if a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and lib.acv_gemm_mma_batched_takes(
+            _p(a), a.stride(0), a.stride(1), _p(w), K, N * K, _p(out), out.stride(0), out.stride(1), N, K):
+        _check(lib.acv_gemm_mma_batched(_p(a), a.stride(0), a.stride(1), _p(w), K, N * K, _p(out), out.stride(0),
+                                        out.stride(1), M, N, K, B, _stream()), "gemm_mma_batched")
+        return out
     _check(library().acv_gemm_simt_batched(_p(a), a.stride(0), a.stride(1), _p(w), K, N * K, _p(out), out.stride(0),
                                            out.stride(1), M, N, K, B, dtype_code(a.dtype), dtype_code(out.dtype), _stream()),
            "gemm_batched")

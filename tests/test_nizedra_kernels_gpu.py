@@ -196,3 +196,22 @@ def test_latent_rows_tensor_core_kernel_refuses_what_it_cannot_hold():
     assert not ops.attention_latent_tc_takes(torch.float32, 8, 144, 128)
     assert not ops.attention_latent_tc_takes(torch.bfloat16, 8, 140, 128)           # rows that are no 16-byte pieces
     assert not ops.attention_latent_tc_takes(torch.bfloat16, 8, 1088, 1024)         # latents too wide for the registers
+
+
+@pytest.mark.parametrize("T,B,K,N,pad_a,pad_c", [(70, 3, 64, 96, 16, 8), (1, 16, 64, 512, 64, 64), (200, 4, 136, 50, 0, 0),
+                                                 (33, 2, 12, 20, 4, 3), (130, 5, 512, 128, 0, 0)])
+def test_per_head_products_over_strided_views(T, B, K, N, pad_a, pad_c):
+    """out[:, b, :] = a[:, b, :] @ w[b]^T on views into wider rows: on the tensor cores where rows are 16-byte pieces,
+    on the CUDA cores otherwise, and in float32; rows past a tile's end and K that is no multiple of the tile."""
+    g = torch.Generator().manual_seed(T + K)
+    a_full = torch.randn(T, B, K + pad_a, generator=g)
+    w = (torch.randn(B, N, K, generator=g) * K ** -0.5)
+    want = torch.einsum("tbk,bnk->tbn", a_full[:, :, :K].to(torch.bfloat16).double(), w.to(torch.bfloat16).double())
+    ref = float(want.abs().max())
+    for dtype, tol in ((torch.bfloat16, 1e-2), (torch.float32, 1e-5)):
+        a = a_full.to(torch.bfloat16).to(dtype).to(DEV)
+        wd = w.to(torch.bfloat16).to(dtype).to(DEV).contiguous()
+        out_full = torch.full((T, B, N + pad_c), 7.0, device=DEV, dtype=dtype)
+        ops.gemm_batched(a[:, :, :K], wd, out_full[:, :, :N])
+        assert float((out_full[:, :, :N].cpu().double() - want).abs().max()) < tol * ref
+        assert bool((out_full[:, :, N:] == 7.0).all())                  # nothing beside the view is written
