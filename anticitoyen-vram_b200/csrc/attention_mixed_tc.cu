@@ -441,6 +441,16 @@ static int launch_mixed_tc(const MixedArgs& a, size_t smem, cudaStream_t stream)
 
 #define MT_SMEM_LIMIT (200 * 1024)
 
+#include "attention_mixed_dec.cuh"
+
+// 1 if one-token requests of these sizes run with a warp a key/value head (attention_mixed_dec.cuh)
+ACV_API int acv_attention_mixed_dec_takes(int NH, int NKV, int D, int DV, int rel_rows) {
+    if (NH <= 0 || NKV <= 0 || NH % NKV || D <= 0 || DV <= 0 || D % 8 || DV % 8 || DV > 128 || D > 512) return 0;
+    MixedArgs a = {};
+    a.NH = NH; a.NKV = NKV; a.D = D; a.DV = DV; a.rel_rows = rel_rows;
+    return mixed_dec_tile(a) > 0;
+}
+
 // 1 if acv_attention_mixed_tc runs these sizes, 0 if they belong to acv_attention_mixed
 ACV_API int acv_attention_mixed_tc_takes(int NH, int NKV, int D, int DV, int rel_rows) {
     if (NH <= 0 || NKV <= 0 || NH % NKV || D <= 0 || DV <= 0 || D % 8 || DV % 8 || DV > 128 || D > 512) return 0;
@@ -479,6 +489,26 @@ ACV_API int acv_attention_mixed_tc(const void* q, int q_stride, void* out, int o
                    temp, cap, rel, bucket_of, n_dist, last_row, rel ? rel_rows : 0, talk, mixed_tc_cluster(NH), n_split,
                    part_acc, part_ml};
     const int ndv = (DV + 15) / 16;
+    // one-token requests: a warp a key/value head where the sizes allow, in a launch of their own
+    const int dec_bn = a.n_dec > 0 ? mixed_dec_tile(a) : 0;
+    if (dec_bn) {
+        const size_t dsmem = mixed_dec_smem(a, dec_bn);
+        int rc = ACV_ERR_SIZE;
+#define MD_CASE(B, N) if (rc == ACV_ERR_SIZE && dec_bn == B && ndv <= N) rc = launch_mixed_dec<B, N>(a, dsmem, stream);
+        MD_CASE(64, 2) MD_CASE(64, 4)
+        MD_CASE(32, 2) MD_CASE(32, 4) MD_CASE(32, 8)
+        MD_CASE(16, 2) MD_CASE(16, 4) MD_CASE(16, 8)
+#undef MD_CASE
+        if (rc) return rc;
+        if (a.n_split > 1) {
+            acv_launch(PDL_ATTN, attn_mixed_merge_kernel, dim3(a.n_dec * NH), dim3(DV < 32 ? 32 : (DV + 31) / 32 * 32), 0, stream,
+                       (const float*)part_acc, (const float*)part_ml, dec_tokens, (bf16*)out, out_stride, a.n_split, NH, DV);
+            if (int e = acv_launch_status()) return e;
+        }
+        if (a.n_tiles == 0) return 0;
+        a.n_dec = 0;
+        a.n_split = 1;
+    }
     // the widest key tile that fits; 64 keys only with few accumulators (registers)
     int BN = 16;
     if (mixed_tc_smem(a, 32) <= MT_SMEM_LIMIT) BN = 32;

@@ -89,6 +89,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_gemm_mma_batched": [P, I, LL, P, I, LL, P, I, LL, I, I, I, I, P],
         "acv_attention_mixed": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P, F, P, P, I, I, P, I, P],
         "acv_attention_mixed_tc_takes": [I, I, I, I, I],
+        "acv_attention_mixed_dec_takes": [I, I, I, I, I],
         "acv_attention_mixed_tc": [P, I, P, I, P, P, P, P, I, P, P, I, P, P, P, I, P, I, I, I, I, I, I, F, I, P, F, P, I, P, I, I, P, I, P, P, P],
         "acv_add_normed_rmsnorm": [P, P, I, P, F, P, F, P, I, I, I, P],
         "acv_cast_rows_f32": [P, I, P, I, I, I, I, P],
@@ -1522,8 +1523,12 @@ def attention_mixed(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v
         n_dec, n_split, acc, ml = work["n_dec"], 1, None, None
         if n_dec:
             seen = min(work["max_dec_kv"], window) if window > 0 else work["max_dec_kv"]
-            clusters = 1 if num_heads <= 16 else (2 if num_heads <= 32 else 4)
-            room = max(1, sm_count(q.device) // (clusters * (n_dec + 8 * work["n_tiles"])))
+            if library().acv_attention_mixed_dec_takes(num_heads, num_kv_heads, head_dim, value_dim, rel_rows):
+                # a launch of their own, a warp a key/value head: small CTAs, several to an SM
+                room = max(1, (3 * sm_count(q.device) // 2) // n_dec)
+            else:
+                clusters = 1 if num_heads <= 16 else (2 if num_heads <= 32 else 4)
+                room = max(1, sm_count(q.device) // (clusters * (n_dec + 8 * work["n_tiles"])))
             n_split = max(1, min(room, seen // MIXED_SPLIT_KEYS, 16))
             if n_split > 1:
                 parts = n_dec * n_split * num_heads
