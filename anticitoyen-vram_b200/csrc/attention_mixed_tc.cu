@@ -93,6 +93,7 @@ attn_mixed_tc_kernel(const MixedArgs a) {
     float* rel_s = tk_s + (size_t)HPC * NH;                                 // [rel_rows][NH]
     float* bias_s = rel_s + (size_t)a.rel_rows * NH;                        // [HPC][BN + 16]: this tile's bias by distance
     constexpr int NDD = BN + 16;
+    int* keyrow_s = reinterpret_cast<int*>(bias_s + (size_t)HPC * NDD);     // [2][BN]: a key's row in kv-head 0 of its page, -1: none
 
     pdl_launch_dependents();
     pdl_wait();
@@ -159,37 +160,43 @@ attn_mixed_tc_kernel(const MixedArgs a) {
     if (a.rel)
         for (int id = tid; id < a.rel_rows * NH; id += nthr) rel_s[id] = a.rel[id];
 
-    // a chunk's place: id = (kvl * BN + r) * CH + c, one division by CH (BN is a power of two); a key's page by a shift
-    // where the page size is a power of two
+    // a chunk's place: id = (kvl * BN + r) * CH + c, one division by CH (BN is a power of two); the place of a tile's
+    // keys in their pages is looked up once per tile, a tile ahead, not once per copied chunk
     const int page_shift = (a.page_size & (a.page_size - 1)) == 0 ? __ffs(a.page_size) - 1 : -1;
-    auto row_of_key = [&](int j, int kvh, bool& ok) -> size_t {
-        const int pi = page_shift >= 0 ? j >> page_shift : j / a.page_size;
-        const int pg = bt[pi];
-        ok = pg >= 0 && pg < a.num_pages;
-        return ((size_t)pg * NKV + kvh) * a.page_size + (j - pi * a.page_size);
+    auto find_rows = [&](int t) {
+        for (int r = tid; r < BN; r += nthr) {
+            const int j = j_first + t * BN + r;
+            int row = -1;
+            if (j <= hi && j >= lo) {
+                const int pi = page_shift >= 0 ? j >> page_shift : j / a.page_size;
+                const int pg = bt[pi];
+                if (pg >= 0 && pg < a.num_pages) row = pg * NKV * a.page_size + (j - pi * a.page_size);
+            }
+            keyrow_s[(t & 1) * BN + r] = row;
+        }
     };
     auto load_keys = [&](int t) {
-        const int j0 = j_first + t * BN;
+        const int* rows_of = keyrow_s + (t & 1) * BN;
         for (int id = tid; id < n_kv * BN * CH; id += nthr) {
             const int rr = id / CH, c = id - rr * CH, r = rr & (BN - 1), kvl = rr / BN;
-            const int j = j0 + r;
-            bool ok = j <= hi && j >= lo && c * 8 < D;
-            size_t off = 0;
-            if (ok) off = row_of_key(j, kv_first + kvl, ok) * D + c * 8;
-            cp_async16(smem_u32(k_s + (size_t)rr * QP + c * 16), ok ? (const void*)(a.k_pages + off) : (const void*)a.k_pages, ok);
+            const int row = rows_of[r];
+            const bool ok = row >= 0 && c * 8 < D;
+            const size_t off = ok ? ((size_t)row + (size_t)(kv_first + kvl) * a.page_size) * D + c * 8 : 0;
+            cp_async16(smem_u32(k_s + (size_t)rr * QP + c * 16), a.k_pages + off, ok);
         }
     };
     auto load_values = [&](int t) {
-        const int j0 = j_first + t * BN;
+        const int* rows_of = keyrow_s + (t & 1) * BN;
         for (int id = tid; id < n_kv * BN * CHV; id += nthr) {
             const int rr = id / CHV, c = id - rr * CHV, r = rr & (BN - 1), kvl = rr / BN;
-            const int j = j0 + r;
-            bool ok = j <= hi && j >= lo && c * 8 < DV;
-            size_t off = 0;
-            if (ok) off = row_of_key(j, kv_first + kvl, ok) * DV + c * 8;
-            cp_async16(smem_u32(v_s + (size_t)rr * VP + c * 16), ok ? (const void*)(a.v_pages + off) : (const void*)a.v_pages, ok);
+            const int row = rows_of[r];
+            const bool ok = row >= 0 && c * 8 < DV;
+            const size_t off = ok ? ((size_t)row + (size_t)(kv_first + kvl) * a.page_size) * DV + c * 8 : 0;
+            cp_async16(smem_u32(v_s + (size_t)rr * VP + c * 16), a.v_pages + off, ok);
         }
     };
+    find_rows(t_first);
+    __syncthreads();
     load_keys(t_first);
     cp_async_commit();
     load_values(t_first);
@@ -226,6 +233,7 @@ attn_mixed_tc_kernel(const MixedArgs a) {
                 bias_s[id] = dist >= 0 ? rel_s[(dist < a.n_dist ? a.bucket_of[dist] : a.last_row) * NH + h_first + w] : 0.f;
             }
         }
+        if (t + 1 < n_t) find_rows(t + 1);
         cp_async_wait<1>();                     // this tile's keys (its values may still be on their way)
         __syncthreads();
         float s[BN / 8][4];
@@ -422,7 +430,7 @@ static size_t mixed_tc_smem(const MixedArgs& a, int BN) {
     const int n_kv = HPC >= group ? HPC / group : 1;
     const size_t QP = ((a.D + 15) & ~15) * 2 + 16, VP = ((a.DV + 15) & ~15) * 2 + 16;
     return (size_t)HPC * MT_ROWS * QP + (size_t)n_kv * BN * (QP + VP) + (size_t)HPC * MT_ROWS * (BN + 8) * 4 +
-           (size_t)HPC * a.NH * 4 + (size_t)a.rel_rows * a.NH * 4 + (size_t)HPC * (BN + 16) * 4;
+           (size_t)HPC * a.NH * 4 + (size_t)a.rel_rows * a.NH * 4 + (size_t)HPC * (BN + 16) * 4 + (size_t)2 * BN * 4;
 }
 
 template <int BN, int NDV>
