@@ -6,7 +6,8 @@
 // the mix reads one row of scores per head.  Where group <= 8 the upper half of the tile is skipped.  The keys of a
 // request may be shared among several CTAs (a.n_split), as in the tile kernel.  A CTA has at least eight warps: those
 // beyond NKV only copy.  The place of a tile's keys in their pages is looked up once per tile (by BN threads, a tile
-// ahead) instead of once per copied 16-byte chunk.
+// ahead) instead of once per copied 16-byte chunk.  Keys and values have two buffers each: the copies of tile t+1 start
+// when tile t's have arrived and run during all of tile t's work, behind two block barriers a tile.
 template <int BN, int NDV>
 __global__ void __launch_bounds__(MT_MAX_WARPS * 32)
 attn_mixed_dec_kernel(const MixedArgs a) {
@@ -18,9 +19,9 @@ attn_mixed_dec_kernel(const MixedArgs a) {
     constexpr int SP = BN + 8;
 
     unsigned char* q_s = smem;                                              // [NKV][16][QP]: row r of warp w is head w*group + r
-    unsigned char* k_s = q_s + (size_t)NKV * MT_ROWS * QP;                  // [NKV][BN][QP]
-    unsigned char* v_s = k_s + (size_t)NKV * BN * QP;                       // [NKV][BN][VP]
-    float* s_s = reinterpret_cast<float*>(v_s + (size_t)NKV * BN * VP);     // [NH][SP]: one row of scores a head
+    unsigned char* k_s = q_s + (size_t)NKV * MT_ROWS * QP;                  // [2][NKV][BN][QP]
+    unsigned char* v_s = k_s + (size_t)2 * NKV * BN * QP;                   // [2][NKV][BN][VP]
+    float* s_s = reinterpret_cast<float*>(v_s + (size_t)2 * NKV * BN * VP); // [NH][SP]: one row of scores a head
     float* tk_s = s_s + (size_t)NH * SP;                                    // [NH][NH] transposed: tk_s[g][h] = talk[h][g]
     float* rel_s = tk_s + (size_t)NH * NH;                                  // [rel_rows][NH]
     float* bias_s = rel_s + (size_t)a.rel_rows * NH;                        // [NH][BN]: this tile's bias of every key
@@ -84,28 +85,29 @@ attn_mixed_dec_kernel(const MixedArgs a) {
     };
     auto load_keys = [&](int t) {
         const int* rows = keyrow_s + (t & 1) * BN;
+        unsigned char* dst = k_s + (size_t)(t & 1) * NKV * BN * QP;
         for (int id = tid; id < NKV * BN * CH; id += nthr) {
             const int rr = id / CH, c = id - rr * CH, r = rr & (BN - 1), kvh = rr / BN;
             const int row = rows[r];
             const bool ok = row >= 0 && c * 8 < D;
             const size_t off = ok ? ((size_t)row + (size_t)kvh * a.page_size) * D + c * 8 : 0;
-            cp_async16(smem_u32(k_s + (size_t)rr * QP + c * 16), a.k_pages + off, ok);
+            cp_async16(smem_u32(dst + (size_t)rr * QP + c * 16), a.k_pages + off, ok);
         }
     };
     auto load_values = [&](int t) {
         const int* rows = keyrow_s + (t & 1) * BN;
+        unsigned char* dst = v_s + (size_t)(t & 1) * NKV * BN * VP;
         for (int id = tid; id < NKV * BN * CHV; id += nthr) {
             const int rr = id / CHV, c = id - rr * CHV, r = rr & (BN - 1), kvh = rr / BN;
             const int row = rows[r];
             const bool ok = row >= 0 && c * 8 < DV;
             const size_t off = ok ? ((size_t)row + (size_t)kvh * a.page_size) * DV + c * 8 : 0;
-            cp_async16(smem_u32(v_s + (size_t)rr * VP + c * 16), a.v_pages + off, ok);
+            cp_async16(smem_u32(dst + (size_t)rr * VP + c * 16), a.v_pages + off, ok);
         }
     };
     find_rows(t_first);
     __syncthreads();
     load_keys(t_first);
-    cp_async_commit();
     load_values(t_first);
     cp_async_commit();
 
@@ -120,8 +122,6 @@ attn_mixed_dec_kernel(const MixedArgs a) {
     const float qk_scale[2] = {a.scale * (a.temp ? a.temp[h_row[0]] : 1.f), a.scale * (a.temp ? a.temp[h_row[1]] : 1.f)};
     const float cap = a.cap, inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
     const uint32_t qb = smem_u32(q_s + (size_t)wk * MT_ROWS * QP);
-    const uint32_t kb = smem_u32(k_s + (size_t)wk * BN * QP);
-    const uint32_t vb = smem_u32(v_s + (size_t)wk * BN * VP);
 
     float acc[2 * NDV][4];
 #pragma unroll
@@ -140,8 +140,15 @@ attn_mixed_dec_kernel(const MixedArgs a) {
             }
         }
         if (t + 1 < n_t) find_rows(t + 1);
-        cp_async_wait<1>();                     // this tile's keys
-        __syncthreads();
+        cp_async_wait<0>();                     // this tile's keys and values
+        __syncthreads();                        // ... and everyone is done with the tile before: its buffers are free
+        if (t + 1 < n_t) {
+            load_keys(t + 1);
+            load_values(t + 1);
+        }
+        cp_async_commit();
+        const uint32_t kb = smem_u32(k_s + ((size_t)(t & 1) * NKV + wk) * BN * QP);
+        const uint32_t vb = smem_u32(v_s + ((size_t)(t & 1) * NKV + wk) * BN * VP);
         float s[BN / 8][4];
 #pragma unroll
         for (int nt = 0; nt < BN / 8; ++nt)
@@ -175,9 +182,7 @@ attn_mixed_dec_kernel(const MixedArgs a) {
                 *reinterpret_cast<float2*>(s_s + (size_t)h_row[hh] * SP + nt * 8 + c_lo) = make_float2(x[0], x[1]);
             }
         }
-        __syncthreads();                        // every head's scores are there; the key buffer is free
-        if (t + 1 < n_t) load_keys(t + 1);
-        cp_async_commit();
+        __syncthreads();                        // every head's scores are there
 #pragma unroll
         for (int nt = 0; nt < BN / 8; ++nt)
 #pragma unroll
@@ -230,8 +235,6 @@ attn_mixed_dec_kernel(const MixedArgs a) {
                 acc[n][2] *= alpha[1]; acc[n][3] *= alpha[1];
             }
         }
-        cp_async_wait<1>();                     // this tile's values
-        __syncthreads();                        // and nobody reads this tile's scores any more
         if (worker)
 #pragma unroll
         for (int kp = 0; kp < BN / 16; ++kp) {
@@ -258,9 +261,6 @@ attn_mixed_dec_kernel(const MixedArgs a) {
                 }
             }
         }
-        __syncthreads();                        // the value buffer is free
-        if (t + 1 < n_t) load_values(t + 1);
-        cp_async_commit();
     }
     cp_async_wait<0>();
 
@@ -295,7 +295,7 @@ attn_mixed_dec_kernel(const MixedArgs a) {
 
 static size_t mixed_dec_smem(const MixedArgs& a, int BN) {
     const size_t QP = ((a.D + 15) & ~15) * 2 + 16, VP = ((a.DV + 15) & ~15) * 2 + 16;
-    return (size_t)a.NKV * MT_ROWS * QP + (size_t)a.NKV * BN * (QP + VP) + (size_t)a.NH * (BN + 8) * 4 + (size_t)a.NH * a.NH * 4 +
+    return (size_t)a.NKV * MT_ROWS * QP + (size_t)2 * a.NKV * BN * (QP + VP) + (size_t)a.NH * (BN + 8) * 4 + (size_t)a.NH * a.NH * 4 +
            (size_t)a.rel_rows * a.NH * 4 + (size_t)a.NH * BN * 4 + (size_t)2 * BN * 4;
 }
 

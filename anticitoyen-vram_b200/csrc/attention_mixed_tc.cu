@@ -177,23 +177,23 @@ attn_mixed_tc_kernel(const MixedArgs a) {
     };
     auto load_keys = [&](int t) {
         const int* rows_of = keyrow_s + (t & 1) * BN;
-        for (int id = tid; id < n_kv * BN * CH; id += nthr) {
-            const int rr = id / CH, c = id - rr * CH, r = rr & (BN - 1), kvl = rr / BN;
+        for_row_chunks(tid, nthr, n_kv * BN, CH, [&](int rr, int c) {
+            const int r = rr & (BN - 1), kvl = rr / BN;
             const int row = rows_of[r];
             const bool ok = row >= 0 && c * 8 < D;
             const size_t off = ok ? ((size_t)row + (size_t)(kv_first + kvl) * a.page_size) * D + c * 8 : 0;
             cp_async16(smem_u32(k_s + (size_t)rr * QP + c * 16), a.k_pages + off, ok);
-        }
+        });
     };
     auto load_values = [&](int t) {
         const int* rows_of = keyrow_s + (t & 1) * BN;
-        for (int id = tid; id < n_kv * BN * CHV; id += nthr) {
-            const int rr = id / CHV, c = id - rr * CHV, r = rr & (BN - 1), kvl = rr / BN;
+        for_row_chunks(tid, nthr, n_kv * BN, CHV, [&](int rr, int c) {
+            const int r = rr & (BN - 1), kvl = rr / BN;
             const int row = rows_of[r];
             const bool ok = row >= 0 && c * 8 < DV;
             const size_t off = ok ? ((size_t)row + (size_t)(kv_first + kvl) * a.page_size) * DV + c * 8 : 0;
             cp_async16(smem_u32(v_s + (size_t)rr * VP + c * 16), a.v_pages + off, ok);
-        }
+        });
     };
     find_rows(t_first);
     __syncthreads();

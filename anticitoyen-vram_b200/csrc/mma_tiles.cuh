@@ -53,6 +53,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// f(row, chunk) for every 16-byte chunk of `rows` rows of `chunks` chunks, spread over the block's threads.  Where the
+// thread count is a multiple of `chunks` a thread keeps its chunk column and walks rows, with no division per chunk.
+template <typename F>
+__device__ __forceinline__ void for_row_chunks(int tid, int nthr, int rows, int chunks, F f) {
+    if (nthr % chunks == 0) {
+        const int c = tid % chunks, step = nthr / chunks;
+#pragma unroll 4
+        for (int rr = tid / chunks; rr < rows; rr += step) f(rr, c);
+    } else {
+        for (int id = tid; id < rows * chunks; id += nthr) {
+            const int rr = id / chunks;
+            f(rr, id - rr * chunks);
+        }
+    }
+}
+
 // address of key `j` of a request in a paged pool [num_pages, NKV, page_size, D]; nullptr if its page is not held
 template <typename T>
 __device__ __forceinline__ const T* paged_row(const T* pages, const int* bt, int j, int kvh, int NKV, int page_size,

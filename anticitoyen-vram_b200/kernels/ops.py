@@ -1524,8 +1524,8 @@ def attention_mixed(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v
         if n_dec:
             seen = min(work["max_dec_kv"], window) if window > 0 else work["max_dec_kv"]
             if library().acv_attention_mixed_dec_takes(num_heads, num_kv_heads, head_dim, value_dim, rel_rows):
-                # a launch of their own, a warp a key/value head: small CTAs, several to an SM
-                room = max(1, (3 * sm_count(q.device) // 2) // n_dec)
+                # a launch of their own, a warp a key/value head; its two buffers of keys and values fill an SM's shared memory
+                room = max(1, sm_count(q.device) // n_dec)
             else:
                 clusters = 1 if num_heads <= 16 else (2 if num_heads <= 32 else 4)
                 room = max(1, sm_count(q.device) // (clusters * (n_dec + 8 * work["n_tiles"])))
