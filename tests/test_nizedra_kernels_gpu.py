@@ -102,6 +102,11 @@ CASES = [
     (8, 2, 64, 64, 64, [600, 900], [40, 1], 0, 16, 500.0, 50.0),
     (4, 4, 16, 24, 16, [1500, 70], [1, 1], 600, 8, 90.0, 0.0),
     (32, 8, 32, 32, 16, [800, 300], [1, 1], 0, 8, 50.0, 20.0),
+    # one-token requests with a warp a key/value head: groups of 3, of 12 (the tile's upper half in part) and of 16
+    (6, 2, 40, 24, 16, [300, 77, 5], [1, 1, 1], 0, 10, 50.0, 20.0),
+    (12, 1, 32, 32, 16, [400, 33], [1, 1], 0, 8, 60.0, 0.0),
+    (16, 1, 64, 64, 64, [700, 130], [1, 1], 90, 0, 0.0, 30.0),
+    (16, 16, 16, 16, 16, [90, 600], [7, 1], 0, 6, 30.0, 10.0),                        # sixteen key/value heads of one head each
 ]
 
 
