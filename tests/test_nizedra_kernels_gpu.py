@@ -107,6 +107,10 @@ CASES = [
     (12, 1, 32, 32, 16, [400, 33], [1, 1], 0, 8, 60.0, 0.0),
     (16, 1, 64, 64, 64, [700, 130], [1, 1], 90, 0, 0.0, 30.0),
     (16, 16, 16, 16, 16, [90, 600], [7, 1], 0, 6, 30.0, 10.0),                        # sixteen key/value heads of one head each
+    # shapes whose one-token requests stay in the tile kernel (more than 16 key/value heads; more than 16 heads to one),
+    # with their keys shared among clusters
+    (40, 40, 16, 16, 16, [700, 300], [1, 1], 0, 10, 40.0, 10.0),
+    (32, 1, 32, 32, 16, [600, 45], [1, 1], 0, 8, 50.0, 20.0),
 ]
 
 
