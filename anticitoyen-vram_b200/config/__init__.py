@@ -5,7 +5,8 @@ from .qwen3 import Qwen3Config
 from .zotonex import ZotonexConfig
 from .redudra import RedudraConfig
 from .nizedra import NizedraConfig
+from .vadelix import VadelixConfig
 from .registry import REGISTRY, ModelFamily, family_of, load_config, register_architecture
 
-__all__ = ["ConfigError", "Qwen3Config", "ZotonexConfig", "RedudraConfig", "NizedraConfig", "REGISTRY", "ModelFamily", "family_of", "load_config",
+__all__ = ["ConfigError", "Qwen3Config", "ZotonexConfig", "RedudraConfig", "NizedraConfig", "VadelixConfig", "REGISTRY", "ModelFamily", "family_of", "load_config",
            "read_config_json", "register_architecture"]

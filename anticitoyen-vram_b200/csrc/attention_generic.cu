@@ -11,7 +11,8 @@
 // j > p - w (mask aligned to absolute positions, acvram/engine/layers.py:1020-1041); with keep_first = f > 0 the
 // first f keys of the request stay visible to every later query, whatever the window (they keep their own
 // positions: nothing is shifted).
-// s = scale * q.k; softmax over the visible keys with a running maximum and sum in
+// s = scale * q.k - slope_h * (p - j) (slopes: one per query head, or none); with sinks (one number per query head) the
+// softmax's denominator also holds exp(sink_h), which has no key and no value.  Softmax over the visible keys with a running maximum and sum in
 // 32-bit (acvram/kernels/acvram_kernels.cu:993-1146 has the same recurrence).
 #include "common.cuh"
 
@@ -22,7 +23,8 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
                                     const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                                     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ bt_rows, int NH, int NKV, int D, int DV,
-                                    int page_size, int num_pages, float scale, int window, int keep_first, int v_row) {
+                                    int page_size, int num_pages, float scale, int window, int keep_first, int v_row,
+                                    const float* __restrict__ sinks, const float* __restrict__ slopes) {
     extern __shared__ float sm_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y * AG_WARPS + warp;
@@ -41,6 +43,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
 #pragma unroll
     for (int r = 0; r < NR; ++r) acc[r] = 0.f;
     float m = -INFINITY, l = 0.f;
+    const float slope = slopes ? slopes[h] : 0.f;
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     // two runs of keys: the kept first ones that the window has passed, [0, min(keep_first, lo)), then [lo, p]
     const int kept = window > 0 ? min(max(keep_first, 0), lo) : 0;
@@ -74,7 +77,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
             } else {
                 for (int e = 0; e < D; ++e) dot = fmaf(qs[e], to_f32(kr[e]), dot);
             }
-            s = dot;
+            s = dot - slope * (float)(p - j);
         }
         const float tmax = warp_max(s);
         if (tmax == -INFINITY) continue;  // uniform: no readable key in this tile
@@ -99,6 +102,14 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
         }
     }
     }
+    if (sinks) {        // a score without key or value: it takes its share of the weights and adds nothing
+        const float sink = sinks[h];
+        const float m_new = fmaxf(m, sink);
+        const float alpha = expf(m - m_new);
+        l = l * alpha + expf(sink - m_new);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) acc[r] *= alpha;
+    }
     T* orow = out + (size_t)t * out_stride + (size_t)h * DV;
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -112,7 +123,7 @@ template <typename T>
 static int launch_generic(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                           const void* v_pages, const int* positions, const int* seq_of_token, const int* block_table,
                           int bt_stride, const int* bt_rows, int T_tokens, int NH, int NKV, int D, int DV, int page_size, int num_pages,
-                          float scale, int window, int keep_first, int v_row, cudaStream_t stream) {
+                          float scale, int window, int keep_first, int v_row, const float* sinks, const float* slopes, cudaStream_t stream) {
     dim3 grid(T_tokens, (NH + AG_WARPS - 1) / AG_WARPS);
     const size_t smem = (size_t)AG_WARPS * D * sizeof(float);
     const int nr = (DV + 31) / 32;
@@ -120,7 +131,7 @@ static int launch_generic(const void* q, int q_stride, void* out, int out_stride
     case N:                                                                                                          \
         attn_generic_kernel<T, N><<<grid, AG_WARPS * 32, smem, stream>>>(                                            \
             (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, positions,             \
-            seq_of_token, block_table, bt_stride, bt_rows, NH, NKV, D, DV, page_size, num_pages, scale, window, keep_first, v_row);                \
+            seq_of_token, block_table, bt_stride, bt_rows, NH, NKV, D, DV, page_size, num_pages, scale, window, keep_first, v_row, sinks, slopes);                \
         break;
     switch (nr) {
         AG_CASE(1) AG_CASE(2) AG_CASE(3) AG_CASE(4) AG_CASE(5) AG_CASE(6) AG_CASE(7) AG_CASE(8)
@@ -135,7 +146,7 @@ ACV_API int acv_attention_generic(const void* q, int q_stride, void* out, int ou
                                   const void* v_pages, const int* positions, const int* seq_of_token,
                                   const int* block_table, int bt_stride, const int* bt_rows, int T_tokens, int NH, int NKV, int D,
                                   int page_size, int num_pages, float scale, int window, int dtype,
-                                  int value_dim, int keep_first, cudaStream_t stream) {
+                                  int value_dim, int keep_first, const float* sinks, const float* slopes, cudaStream_t stream) {
     if (T_tokens <= 0) return 0;
     const int DV = value_dim > 0 ? value_dim : D;
     if (D <= 0 || D > 1024 || DV > 512 || NKV <= 0 || NH % NKV) return ACV_ERR_SIZE;
@@ -145,10 +156,10 @@ ACV_API int acv_attention_generic(const void* q, int q_stride, void* out, int ou
     if (dtype == ACV_F32)
         return launch_generic<float>(q, q_stride, out, out_stride, k_pages, v_pages, positions, seq_of_token,
                                      block_table, bt_stride, bt_rows, T_tokens, NH, NKV, D, DV, page_size, num_pages, scale, window,
-                                     keep_first, v_row, stream);
+                                     keep_first, v_row, sinks, slopes, stream);
     if (dtype == ACV_BF16)
         return launch_generic<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, positions, seq_of_token,
                                     block_table, bt_stride, bt_rows, T_tokens, NH, NKV, D, DV, page_size, num_pages, scale, window,
-                                    keep_first, v_row, stream);
+                                    keep_first, v_row, sinks, slopes, stream);
     return ACV_ERR_DTYPE;
 }

@@ -21,6 +21,7 @@
 
 // gated activation of an expert (ops.GLU_*)
 #define GLU_SWISH_CLAMPED 0  // g = min(a, limit), u = clamp(b, -limit, limit): g * sigmoid(alpha g) * (u + 1)
+// acv_glu also takes 1, 2, 3: act(a) * b with act the plain activation of that number (gelu_tanh, silu, gelu)
 
 template <typename T> __device__ __forceinline__ float sigmoid_f32(float x);
 template <> __device__ __forceinline__ float sigmoid_f32<float>(float x) { return 1.f / (1.f + expf(-x)); }
@@ -33,6 +34,14 @@ __device__ __forceinline__ float glu_act(float a, float b, float limit, float al
     return g * sigmoid_f32<T>(alpha * g) * (u + 1.f);
 }
 
+// activation of an expert that has no gate: y = act(W_up x), out = W_down y  (ops.ACTIVATIONS)
+__device__ __forceinline__ float plain_act(float z, int kind) {
+    if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (kind == 2) return z / (1.f + expf(-z));
+    if (kind == 3) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
+    return z;
+}
+
 // ----------------------------------------------------------------------------- routing
 #define MR_WARPS 4
 // scores in shared memory, E floats per warp.  ids/weights: [T, top].  gate_w (optional, [H]): the shared
@@ -43,7 +52,7 @@ template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, int h_stride, const float* __restrict__ w_router,
                                  const float* __restrict__ gate_w, const float* __restrict__ z, int ldz, int T_tokens, int H,
                                  int E, int top, int softmax, int renorm, int* __restrict__ ids, float* __restrict__ weights,
-                                 float* __restrict__ gate) {
+                                 float* __restrict__ gate, int n_groups, int keep_groups, float renorm_eps) {
     extern __shared__ float sm_all[];
     pdl_launch_dependents();
     pdl_wait();
@@ -88,6 +97,29 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int h_stride, const fl
         for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
     }
     __syncwarp();
+    if (n_groups > 1 && keep_groups < n_groups) {
+        // The experts stand in n_groups equal groups of neighbours; a group is worth its best score, and only the
+        // keep_groups best groups (ties: the lower index) can be chosen from.  Lane g holds group g's worth.
+        const int per = E / n_groups;
+        float worth = -INFINITY;
+        if (lane < n_groups)
+            for (int e = lane * per; e < (lane + 1) * per; ++e) worth = fmaxf(worth, sc[e]);
+        unsigned kept = 0;
+        for (int j = 0; j < keep_groups; ++j) {
+            float best = (kept >> lane) & 1u ? -INFINITY : worth;
+            int arg = lane < n_groups && !((kept >> lane) & 1u) ? lane : 0x7fffffff;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
+            }
+            if (arg != 0x7fffffff) kept |= 1u << arg;
+        }
+        for (int e = lane; e < E; e += 32)
+            if (!((kept >> (e / per)) & 1u)) sc[e] = -INFINITY;
+        __syncwarp();
+    }
     float total = 0.f;
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY;
@@ -112,22 +144,24 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int h_stride, const fl
         __syncwarp();
     }
     if (renorm && lane == 0)
-        for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= total;
+        for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= total + renorm_eps;
 }
 
 ACV_API int acv_moe_route(const void* h, int h_stride, const float* w_router, const float* gate_w, const float* z, int ldz,
                           int T_tokens, int H, int E, int top, int softmax, int renorm, int* ids, float* weights, float* gate,
-                          int dtype, cudaStream_t stream) {
+                          int dtype, int n_groups, int keep_groups, float renorm_eps, cudaStream_t stream) {
     if (T_tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || E > 4096) return ACV_ERR_SIZE;
+    if (n_groups < 1) n_groups = 1;
+    if (n_groups > 32 || E % n_groups || keep_groups < 1 || (n_groups > 1 && top > keep_groups * (E / n_groups))) return ACV_ERR_SIZE;
     const size_t smem = (size_t)MR_WARPS * E * sizeof(float);
     const int grid = (T_tokens + MR_WARPS - 1) / MR_WARPS;
     if (dtype == ACV_F32)
         acv_launch(PDL_MISC, moe_route_kernel<float>, grid, MR_WARPS * 32, smem, stream, (const float*)h, h_stride, w_router,
-                   gate_w, z, ldz, T_tokens, H, E, top, softmax, renorm, ids, weights, gate);
+                   gate_w, z, ldz, T_tokens, H, E, top, softmax, renorm, ids, weights, gate, n_groups, keep_groups, renorm_eps);
     else if (dtype == ACV_BF16)
         acv_launch(PDL_MISC, moe_route_kernel<bf16>, grid, MR_WARPS * 32, smem, stream, (const bf16*)h, h_stride, w_router,
-                   gate_w, z, ldz, T_tokens, H, E, top, softmax, renorm, ids, weights, gate);
+                   gate_w, z, ldz, T_tokens, H, E, top, softmax, renorm, ids, weights, gate, n_groups, keep_groups, renorm_eps);
     else
         return ACV_ERR_DTYPE;
     return acv_launch_status();
@@ -248,11 +282,12 @@ ACV_API int acv_moe_gather(const void* h, int ldh, const int* grouped, const flo
 // else: A's row r is row r of the grouped list itself (the activations of the product before); output float,
 //      multiplied by the row's weight when given (the weight on the expert's output).
 // Sums run over k in ascending order inside fixed slabs of 16: a row's result does not depend on the others.
-template <typename T, bool GLU>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_gemm_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, long long w_expert_stride, int ldw,
                      void* __restrict__ C, int ldc, const int* __restrict__ grouped, const int* __restrict__ tile_expert,
                      const float* __restrict__ row_weight, int top, int N, int K, float limit, float alpha, int pairs) {
+    constexpr bool GLU = MODE == 1, GATHER = MODE != 0;
     __shared__ float As[16][MOE_TILE + 4];
     __shared__ float Ws[16][64 + 4];
     __shared__ float Us[GLU ? 16 : 1][64 + 4];
@@ -283,7 +318,7 @@ moe_gemm_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, 
             const int r = idx >> 4, kk = idx & 15;
             const int gk = k0 + kk, gn = n0 + r;
             const int s = src[r];
-            const long long arow = GLU ? (s >= 0 ? s / top : -1) : (s >= 0 ? tile * MOE_TILE + r : -1);
+            const long long arow = GATHER ? (s >= 0 ? s / top : -1) : (s >= 0 ? tile * MOE_TILE + r : -1);
             As[kk][r] = (arow >= 0 && gk < K) ? to_f32(A[(size_t)arow * lda + gk]) : 0.f;
             Ws[kk][r] = (gn < N && gk < K) ? to_f32(We[(size_t)(GLU && pairs ? 2 * gn : gn) * ldw + gk]) : 0.f;
             if constexpr (GLU) Us[kk][r] = (gn < N && gk < K) ? to_f32(We[(size_t)(pairs ? 2 * gn + 1 : N + gn) * ldw + gk]) : 0.f;
@@ -322,13 +357,16 @@ moe_gemm_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, 
             if (gn >= N) continue;
             if constexpr (GLU)
                 ((T*)C)[crow + gn] = from_f32<T>(glu_act<T>(acc[i][j] * w, acu[i][j] * w, limit, alpha));
+            else if constexpr (MODE == 2)
+                ((T*)C)[crow + gn] = from_f32<T>(plain_act(acc[i][j] * w, pairs));
             else
                 ((float*)C)[crow + gn] = acc[i][j] * w;
         }
     }
 }
 
-// which: 0 = gate/up with activation (C of A's type), 1 = down (C float)
+// which: 0 = gate/up with the gated activation (C of A's type), 1 = down (C float), 2 = up alone with a plain activation
+// (C of A's type; the activation's kind travels in `pairs`)
 ACV_API int acv_moe_gemm_simt(const void* A, int lda, const void* W, long long w_expert_stride, int ldw, void* C, int ldc,
                               const int* grouped, const int* tile_expert, const float* row_weight, int top, int max_tiles,
                               int N, int K, int which, float limit, float alpha, int pairs, int dtype, cudaStream_t stream) {
@@ -339,9 +377,9 @@ ACV_API int acv_moe_gemm_simt(const void* A, int lda, const void* W, long long w
     acv_launch(PDL_GEMM, moe_gemm_simt_kernel<TT, G>, grid, 256, 0, stream, (const TT*)A, lda, (const TT*)W,          \
                w_expert_stride, ldw, C, ldc, grouped, tile_expert, row_weight, top, N, K, limit, alpha, pairs)
     if (dtype == ACV_F32) {
-        if (which == 0) MG_LAUNCH(float, true); else MG_LAUNCH(float, false);
+        if (which == 0) MG_LAUNCH(float, 1); else if (which == 2) MG_LAUNCH(float, 2); else MG_LAUNCH(float, 0);
     } else if (dtype == ACV_BF16) {
-        if (which == 0) MG_LAUNCH(bf16, true); else MG_LAUNCH(bf16, false);
+        if (which == 0) MG_LAUNCH(bf16, 1); else if (which == 2) MG_LAUNCH(bf16, 2); else MG_LAUNCH(bf16, 0);
     } else {
         return ACV_ERR_DTYPE;
     }
@@ -361,12 +399,13 @@ ACV_API int acv_moe_gemm_simt(const void* A, int lda, const void* W, long long w
 #define MM_THREADS 128
 #define MM_STAGES 3
 
-template <bool GLU>
+template <int MODE>
 __global__ void __launch_bounds__(MM_THREADS)
 moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, long long w_expert_stride, int ldw,
                     void* __restrict__ C, int ldc, const int* __restrict__ grouped, const int* __restrict__ tile_expert,
                     const float* __restrict__ row_weight, int top, int N, int K, float limit, float alpha, int pairs) {
     extern __shared__ __align__(128) unsigned char mm_smem[];
+    constexpr bool GLU = MODE == 1, GATHER = MODE != 0;
     constexpr int A_BYTES = MOE_TILE * MM_BK * 2;
     constexpr int W_BYTES = MM_BN * MM_BK * 2;
     constexpr int STAGE = A_BYTES + (GLU ? 2 : 1) * W_BYTES;
@@ -395,7 +434,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict_
             const int id = tid + it * MM_THREADS;
             const int r = id >> 3, c = id & 7;
             const int s = src[r];
-            const long long arow = GLU ? (s >= 0 ? s / top : -1) : (s >= 0 ? (long long)tile * MOE_TILE + r : -1);
+            const long long arow = GATHER ? (s >= 0 ? s / top : -1) : (s >= 0 ? (long long)tile * MOE_TILE + r : -1);
             const bool ok = arow >= 0 && k0 + c * 8 < K;
             cp_async16(smem_u32(base + tile_off<MM_BK>(r, c)), ok ? (const void*)(A + arow * lda + k0 + c * 8) : (const void*)A, ok);
         }
@@ -471,6 +510,8 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict_
                 const float v = acc[nt][half * 2 + e] * w;
                 if constexpr (GLU)
                     ((bf16*)C)[crow + col] = __float2bfloat16_rn(glu_act<bf16>(v, acu[nt][half * 2 + e] * w, limit, alpha));
+                else if constexpr (MODE == 2)
+                    ((bf16*)C)[crow + col] = __float2bfloat16_rn(plain_act(v, pairs));
                 else
                     ((float*)C)[crow + col] = v;
             }
@@ -478,7 +519,8 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict_
     }
 }
 
-// which: 0 = gate/up with activation (C bfloat16), 1 = down (C float)
+// which: 0 = gate/up with the gated activation (C bfloat16), 1 = down (C float), 2 = up alone with a plain activation
+// (C bfloat16; the activation's kind travels in `pairs`)
 ACV_API int acv_moe_gemm_mma(const void* A, int lda, const void* W, long long w_expert_stride, int ldw, void* C, int ldc,
                              const int* grouped, const int* tile_expert, const float* row_weight, int top, int max_tiles,
                              int N, int K, int which, float limit, float alpha, int pairs, cudaStream_t stream) {
@@ -489,14 +531,21 @@ ACV_API int acv_moe_gemm_mma(const void* A, int lda, const void* W, long long w_
     if (which == 0) {
         const int smem = MM_STAGES * (MOE_TILE * MM_BK * 2 + 2 * MM_BN * MM_BK * 2);
         static AcvSmemConfig cfg;
-        if (int rc = acv_ensure_smem(cfg, moe_gemm_mma_kernel<true>, smem)) return rc;
-        acv_launch(PDL_GEMM, moe_gemm_mma_kernel<true>, grid, MM_THREADS, smem, stream, (const bf16*)A, lda, (const bf16*)W,
+        if (int rc = acv_ensure_smem(cfg, moe_gemm_mma_kernel<1>, smem)) return rc;
+        acv_launch(PDL_GEMM, moe_gemm_mma_kernel<1>, grid, MM_THREADS, smem, stream, (const bf16*)A, lda, (const bf16*)W,
                    w_expert_stride, ldw, C, ldc, grouped, tile_expert, row_weight, top, N, K, limit, alpha, pairs);
     } else {
         const int smem = MM_STAGES * (MOE_TILE * MM_BK * 2 + MM_BN * MM_BK * 2);
         static AcvSmemConfig cfg;
-        if (int rc = acv_ensure_smem(cfg, moe_gemm_mma_kernel<false>, smem)) return rc;
-        acv_launch(PDL_GEMM, moe_gemm_mma_kernel<false>, grid, MM_THREADS, smem, stream, (const bf16*)A, lda, (const bf16*)W,
+        if (which == 2) {
+            static AcvSmemConfig cfg2;
+            if (int rc = acv_ensure_smem(cfg2, moe_gemm_mma_kernel<2>, smem)) return rc;
+            acv_launch(PDL_GEMM, moe_gemm_mma_kernel<2>, grid, MM_THREADS, smem, stream, (const bf16*)A, lda, (const bf16*)W,
+                       w_expert_stride, ldw, C, ldc, grouped, tile_expert, row_weight, top, N, K, limit, alpha, pairs);
+            return acv_launch_status();
+        }
+        if (int rc = acv_ensure_smem(cfg, moe_gemm_mma_kernel<0>, smem)) return rc;
+        acv_launch(PDL_GEMM, moe_gemm_mma_kernel<0>, grid, MM_THREADS, smem, stream, (const bf16*)A, lda, (const bf16*)W,
                    w_expert_stride, ldw, C, ldc, grouped, tile_expert, row_weight, top, N, K, limit, alpha, pairs);
     }
     return acv_launch_status();
@@ -582,14 +631,14 @@ ACV_API int acv_moe_combine(const void* D, int ldd, int d_dtype, const int* plac
 // token, e.g. a shared expert).
 template <typename T>
 __global__ void glu_kernel(const T* __restrict__ gu, int ldg, T* __restrict__ out, int ldo, int I, size_t total, float limit,
-                           float alpha, int pairs) {
+                           float alpha, int pairs, int kind) {
     pdl_launch_dependents();
     pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
         const int i = (int)(idx - t * I);
         const float a = to_f32(gu[t * ldg + (pairs ? 2 * i : i)]), b = to_f32(gu[t * ldg + (pairs ? 2 * i + 1 : I + i)]);
-        out[t * ldo + i] = from_f32<T>(glu_act<T>(a, b, limit, alpha));
+        out[t * ldo + i] = from_f32<T>(kind == GLU_SWISH_CLAMPED ? glu_act<T>(a, b, limit, alpha) : plain_act(a, kind) * b);
     }
 }
 
@@ -597,12 +646,12 @@ ACV_API int acv_glu(const void* gu, int ldg, void* out, int ldo, int T_tokens, i
                     int pairs, int dtype, cudaStream_t stream) {
     const size_t total = (size_t)T_tokens * I;
     if (total == 0) return 0;
-    if (kind != GLU_SWISH_CLAMPED) return ACV_ERR_SIZE;
+    if (kind < 0 || kind > 3) return ACV_ERR_SIZE;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (dtype == ACV_F32)
-        acv_launch(PDL_ACT, glu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, ldg, (float*)out, ldo, I, total, limit, alpha, pairs);
+        acv_launch(PDL_ACT, glu_kernel<float>, blocks, 256, 0, stream, (const float*)gu, ldg, (float*)out, ldo, I, total, limit, alpha, pairs, kind);
     else if (dtype == ACV_BF16)
-        acv_launch(PDL_ACT, glu_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, ldg, (bf16*)out, ldo, I, total, limit, alpha, pairs);
+        acv_launch(PDL_ACT, glu_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, ldg, (bf16*)out, ldo, I, total, limit, alpha, pairs, kind);
     else
         return ACV_ERR_DTYPE;
     return acv_launch_status();

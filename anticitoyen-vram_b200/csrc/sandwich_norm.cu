@@ -95,9 +95,11 @@ ACV_API int acv_cast_rows_f32(const float* x, int ld_x, void* out, int ld_out, i
 //         layer's two learned numbers, folded by the caller)
 // kind 1: gelu_tanh: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 // kind 2: silu
+// kind 3: gelu (exact): 0.5 z (1 + erf(z / sqrt 2))
 __device__ __forceinline__ float activation_f32(float z, int kind, float p0, float p1) {
     if (kind == 0) return z > 0.f ? fmaf(p0 * z, z, 0.5f * z) : fmaf(p1, expm1f(z) - z, 0.5f * z);
     if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (kind == 3) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
     return z / (1.f + expf(-z));
 }
 
@@ -129,7 +131,7 @@ __global__ void activation_bf16x8_kernel(const uint4* __restrict__ in, uint4* __
 
 ACV_API int acv_activation(const void* in, void* out, long long n, int kind, float p0, float p1, int dtype, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (kind < 0 || kind > 2) return ACV_ERR_SIZE;
+    if (kind < 0 || kind > 3) return ACV_ERR_SIZE;
     if (dtype == ACV_BF16 && (n & 7) == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         const size_t n8 = (size_t)n / 8;
         const int blocks = (int)((n8 + 255) / 256 < 148 * 8 ? (n8 + 255) / 256 : 148 * 8);

@@ -61,6 +61,7 @@ class StepContext:
     q_lens: list[int] = field(default_factory=list)
     kv_lens: list[int] = field(default_factory=list)
     work: dict = field(default_factory=dict)   # provider key -> what that kind of mixer asked for (device views, counts)
+    shared: dict = field(default_factory=dict) # what a layer leaves for later layers of the same step (key -> tensor)
 
     @property
     def max_q_len(self) -> int:

@@ -71,7 +71,14 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_swiglu": [P, P, I, I, I, P],
         "acv_add_bias": [P, I, P, I, I, I, P],
         "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, P, I, I, I, I, F, P],
-        "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, I, P],
+        "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P],
+        "acv_add_group_rmsnorm": [P, P, F, P, P, P, I, I, I, F, I, I, P],
+        "acv_input_conv": [P, P, P, P, P, P, P, I, I, I, I, P],
+        "acv_add_group_rmsnorm_conv": [P, P, F, P, P, P, P, P, I, I, I, F, I, I, I, P],
+        "acv_qkv_prepare": [P, I, I, I, I, I, I, P, P, F, P, I, I, F, I, I, F, P, I, F, P, P, P, I, P, P, P, I, I, I, P],
+        "acv_token_shift_multi": [P, P, P, P, P, P, P, I, I, I, I, P],
+        "acv_wkv_decay": [P, I, P, P, P, I, I, I, P],
+        "acv_wkv": [P, P, P, I, P, P, P, P, P, P, P, I, P, P, I, P, I, I, I, I, I, I, P],
         "acv_add_layernorm": [P, P, F, P, P, P, P, I, I, F, I, I, P],
         "acv_token_shift": [P, P, P, P, P, P, P, I, I, I, P],
         "acv_add_layernorm_shift": [P, P, F, P, P, P, P, P, P, I, I, F, I, I, P],
@@ -111,7 +118,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_heads_norm_append": [P, P, I, P, P, I, I, I, I, I, I, I, P, P, F, P, P, P, I, P, P, P, I, I, I, P],
         "acv_diff_combine": [P, I, I, P, I, I, I, I, F, F, F, I, P],
         "acv_diff_attention_generic": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, F, F, F, I, P],
-        "acv_moe_route": [P, I, P, P, P, I, I, I, I, I, I, I, P, P, P, I, P],
+        "acv_moe_route": [P, I, P, P, P, I, I, I, I, I, I, I, P, P, P, I, I, I, F, P],
         "acv_moe_group": [P, I, I, I, I, P, P, P, P, P],
         "acv_moe_gather": [P, I, P, P, I, I, P, P, P, I, I, P],
         "acv_gemm_tc_grouped": [P, I, P, I, P, I, I, I, I, I, P, P, I, I, P, F, F, I, P, I, I, P],
@@ -305,19 +312,30 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
         dtype_code(qkv.dtype), int(value_dim), float(v_scale), _stream()), "qk_norm_rope_append")
 
 
+def _head_vectors(num_heads: int, *vectors) -> None:
+    for v in vectors:
+        if v is not None and (v.dtype != torch.float32 or v.numel() != num_heads or not v.is_contiguous() or not v.is_cuda):
+            raise KernelError("attention: sinks and slopes are contiguous float32 vectors with one number per query head")
+
+
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                       num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-                      table_rows: torch.Tensor | None = None, value_dim: int = 0, keep_first: int = 0) -> torch.Tensor:
+                      table_rows: torch.Tensor | None = None, value_dim: int = 0, keep_first: int = 0,
+                      sinks: torch.Tensor | None = None, slopes: torch.Tensor | None = None) -> torch.Tensor:
     """Paged causal attention for every token of the step.  q: rows of num_heads*head_dim (row stride free).
     ``value_dim`` > 0: value rows (and the result's heads) of that size; ``keep_first``: the first keys of a request
-    that stay visible behind the window."""
+    that stay visible behind the window.  ``sinks`` (float32 [num_heads]): exp(sink_h) joins the softmax's denominator
+    (a score with no key and no value); ``slopes`` (float32 [num_heads]): slope_h * (i - j) is taken off the score of
+    query i and key j."""
     _need_cuda(q, out, k_pages)
+    _head_vectors(num_heads, sinks, slopes)
     T = q.shape[0]
     _check(library().acv_attention_generic(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(positions), _p(seq_of_token),
         _p(block_table), block_table.stride(0), _p(table_rows), T, num_heads, num_kv_heads, head_dim, k_pages.shape[2],
-        k_pages.shape[0], scale, window, dtype_code(q.dtype), int(value_dim), int(keep_first), _stream()), "attention_generic")
+        k_pages.shape[0], scale, window, dtype_code(q.dtype), int(value_dim), int(keep_first), _p(sinks), _p(slopes), _stream()),
+           "attention_generic")
     return out
 
 
@@ -830,11 +848,13 @@ def attention_work_decode(padded: int, max_kv: int) -> tuple[dict, dict]:
 def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx,
               block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: int = 0, work: dict | None = None, chunk: int = 0, value_dim: int = 0,
-              keep_first: int = 0) -> torch.Tensor:
+              keep_first: int = 0, sinks: torch.Tensor | None = None, slopes: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of every token of the step over its request's pages.  A query sees the keys at or before its
     position; with ``window`` > 0 the last ``window`` of them, and with ``keep_first`` > 0 also the first
     ``keep_first`` keys of the request; with ``chunk`` > 0 those of its own chunk of ``chunk``
     positions counted from the request's position 0.  ``value_dim``: the size of a value row where it is not ``head_dim``.
+    ``sinks`` (float32 [heads]): exp(sink_h) joins the softmax's denominator; ``slopes`` (float32 [heads]): the score of
+    query i and key j loses slope_h (i - j).
 
     ``qkv`` is the stacked projection after norm and rotation (queries are its first
     num_heads*head_dim columns); ``ctx`` is the step's StepContext; ``work`` the step's work lists
@@ -853,12 +873,14 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
     # kept first keys: the split-KV decode kernel and the tcgen05 portion kernel know them, the mma.sync portion kernel does not
     if not generic and keep_first > 0 and (chunk > 0 or (w["n_tiles"] and not attention_tc_takes(qkv, out, k_pages, head_dim))):
         generic = True
+    if sinks is not None or slopes is not None:
+        generic = True
     if generic:
         if chunk > 0:
             raise KernelError("attention: the chunked mask is built for the tensor-core kernels' sizes only")
         return attention_generic(qkv, out, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, num_heads,
                                  num_kv_heads, head_dim, scale, window, table_rows=rows, value_dim=value_dim,
-                                 keep_first=keep_first)
+                                 keep_first=keep_first, sinks=sinks, slopes=slopes)
     if w["n_dec"]:
         kv = min(w["max_dec_kv"], window + keep_first) if window > 0 else w["max_dec_kv"]
         kv = min(kv, chunk) if chunk > 0 else kv
@@ -1094,23 +1116,27 @@ def moe_max_tiles(rows: int, experts: int, tile: int = MOE_TILE) -> int:
 
 def moe_route(h: torch.Tensor, w_router: torch.Tensor | None, gate_w: torch.Tensor | None, top: int, softmax: bool, renorm: bool,
               ids: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor | None, logits: torch.Tensor | None = None,
-              experts: int | None = None) -> None:
+              experts: int | None = None, groups: tuple[int, int] | None = None, renorm_eps: float = 0.0) -> None:
     """Router of a mixture of experts, in 32-bit: ids, weights [T, top] (int32, float32); gate [T] = sigmoid(h . gate_w).
     With ``logits`` (float32 [T, >= experts (+ 1)]: the router's columns, then the gate's) the products were made before
-    and only the scores and the choice are made here."""
+    and only the scores and the choice are made here.  ``groups`` = (count, keep): the experts stand in ``count`` equal
+    groups of neighbours, a group is worth its best score, and only experts of the ``keep`` best groups can be chosen.
+    ``renorm_eps`` joins the sum that the chosen scores are divided by."""
     _need_cuda(h, ids, weights)
     T, H = h.shape
+    n_groups, keep = (int(groups[0]), int(groups[1])) if groups else (1, 1)
     if logits is not None:
         if logits.dtype != torch.float32 or logits.stride(1) != 1 or experts is None:
             raise KernelError("moe_route: float32 logits and the number of experts are wanted")
         _check(library().acv_moe_route(None, 0, None, None, _p(logits), logits.stride(0), T, H, experts, top, int(softmax),
-                                       int(renorm), _p(ids), _p(weights), _p(gate), dtype_code(h.dtype), _stream()), "moe_route")
+                                       int(renorm), _p(ids), _p(weights), _p(gate), dtype_code(h.dtype), n_groups, keep, float(renorm_eps),
+                                       _stream()), "moe_route")
         return
     if w_router.dtype != torch.float32 or not w_router.is_contiguous() or h.stride(1) != 1:
         raise KernelError("moe_route: a contiguous float32 router matrix is wanted")
     _check(library().acv_moe_route(_p(h), h.stride(0), _p(w_router), _p(gate_w), None, 0, T, H, w_router.shape[0], top,
-                                   int(softmax), int(renorm), _p(ids), _p(weights), _p(gate), dtype_code(h.dtype), _stream()),
-           "moe_route")
+                                   int(softmax), int(renorm), _p(ids), _p(weights), _p(gate), dtype_code(h.dtype), n_groups, keep,
+                                   float(renorm_eps), _stream()), "moe_route")
 
 
 def moe_group(ids: torch.Tensor, experts: int, grouped: torch.Tensor, place: torch.Tensor, tile_expert: torch.Tensor,
@@ -1159,11 +1185,22 @@ def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_ex
     return out
 
 
+def _moe_which(glu: bool, plain_act: str | None, pairs) -> tuple[int, int]:
+    """(which product of the grouped kernels, what travels in their ``pairs`` argument)."""
+    if plain_act is None:
+        return (0 if glu else 1), int(pairs)
+    if glu or plain_act not in ACTIVATIONS or ACTIVATIONS[plain_act] == 0:
+        raise KernelError(f"grouped products: no plain activation '{plain_act}' (or asked for beside a gate)")
+    return 2, ACTIVATIONS[plain_act]
+
+
 def moe_gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
                   row_weight: torch.Tensor | None, top: int, glu: bool, limit: float = 0.0, alpha: float = 0.0,
-                  pairs: bool = False) -> torch.Tensor:
+                  pairs: bool = False, plain_act: str | None = None) -> torch.Tensor:
     """The experts' products over the grouped rows on the CUDA cores, 32-bit accumulation.  ``pairs``: with ``glu``, the
-    rows of w are (gate, up) pairs instead of all gate rows followed by all up rows.
+    rows of w are (gate, up) pairs instead of all gate rows followed by all up rows.  ``plain_act`` (a name of
+    ``ACTIVATIONS``; not with ``glu``): experts without a gate: w [E, N, K], a [T, K] the tokens, out
+    [tiles * MOE_TILE, N] of a's type = act(w a).
 
     ``glu``: w [E, 2N, K] (gate rows, then up rows), a [T, K] the tokens, out [tiles * MOE_TILE, N] of a's type =
     act(weight * gate, weight * up).  Otherwise w [E, N, K], a the grouped rows [tiles * MOE_TILE, K], out float32
@@ -1171,12 +1208,13 @@ def moe_gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, grouped: 
     _need_cuda(a, w, out, grouped, tile_expert)
     E, NW, K = w.shape
     N = NW // 2 if glu else NW
+    which, pairs = _moe_which(glu, plain_act, pairs)
     if a.shape[1] != K or out.shape[1] != N or a.dtype != w.dtype or not w.is_contiguous() or a.stride(1) != 1 or \
-            out.stride(1) != 1 or out.dtype != (a.dtype if glu else torch.float32):
+            out.stride(1) != 1 or out.dtype != (a.dtype if which != 1 else torch.float32):
         raise KernelError(f"moe_gemm_simt: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
     _check(library().acv_moe_gemm_simt(_p(a), a.stride(0), _p(w), w.stride(0), w.stride(1), _p(out), out.stride(0),
                                        _p(grouped), _p(tile_expert), _p(row_weight), top, tile_expert.numel(), N, K,
-                                       0 if glu else 1, limit, alpha, int(pairs), dtype_code(a.dtype), _stream()), "moe_gemm_simt")
+                                       which, limit, alpha, int(pairs), dtype_code(a.dtype), _stream()), "moe_gemm_simt")
     return out
 
 
@@ -1189,25 +1227,29 @@ def moe_gemm_mma_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 def moe_gemm_mma(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
                  row_weight: torch.Tensor | None, top: int, glu: bool, limit: float = 0.0, alpha: float = 0.0,
-                 pairs: bool = False) -> torch.Tensor:
+                 pairs: bool = False, plain_act: str | None = None) -> torch.Tensor:
     """``moe_gemm_simt`` on the tensor cores (bfloat16 operands, float accumulators; the same arguments)."""
     _need_cuda(a, w, out, grouped, tile_expert)
     E, NW, K = w.shape
     N = NW // 2 if glu else NW
-    if a.shape[1] != K or out.shape[1] != N or out.stride(1) != 1 or out.dtype != (torch.bfloat16 if glu else torch.float32):
+    which, pairs = _moe_which(glu, plain_act, pairs)
+    if a.shape[1] != K or out.shape[1] != N or out.stride(1) != 1 or out.dtype != (torch.bfloat16 if which != 1 else torch.float32):
         raise KernelError(f"moe_gemm_mma: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
     _check(library().acv_moe_gemm_mma(_p(a), a.stride(0), _p(w), w.stride(0), w.stride(1), _p(out), out.stride(0),
                                       _p(grouped), _p(tile_expert), _p(row_weight), top, tile_expert.numel(), N, K,
-                                      0 if glu else 1, limit, alpha, int(pairs), _stream()), "moe_gemm_mma")
+                                      which, limit, alpha, int(pairs), _stream()), "moe_gemm_mma")
     return out
 
 
 def moe_experts_up(h: torch.Tensor, gate_up: torch.Tensor, act: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
-                   row_weight: torch.Tensor | None, top: int, limit: float, alpha: float, pairs: bool = False) -> torch.Tensor:
-    """act[grouped row] = gated activation of the row's expert's gate and up products of its token; dispatch by shape."""
+                   row_weight: torch.Tensor | None, top: int, limit: float, alpha: float, pairs: bool = False,
+                   plain_act: str | None = None) -> torch.Tensor:
+    """act[grouped row] = gated activation of the row's expert's gate and up products of its token (with ``plain_act``:
+    that activation of the expert's one up product); dispatch by shape."""
+    glu = plain_act is None
     if moe_gemm_mma_takes(h, gate_up):
-        return moe_gemm_mma(h, gate_up, act, grouped, tile_expert, row_weight, top, True, limit, alpha, pairs)
-    return moe_gemm_simt(h, gate_up, act, grouped, tile_expert, row_weight, top, True, limit, alpha, pairs)
+        return moe_gemm_mma(h, gate_up, act, grouped, tile_expert, row_weight, top, glu, limit, alpha, pairs, plain_act)
+    return moe_gemm_simt(h, gate_up, act, grouped, tile_expert, row_weight, top, glu, limit, alpha, pairs, plain_act)
 
 
 def moe_experts_down(act: torch.Tensor, down: torch.Tensor, out: torch.Tensor, grouped: torch.Tensor, tile_expert: torch.Tensor,
@@ -1231,7 +1273,8 @@ def moe_combine(d: torch.Tensor, place: torch.Tensor, top: int, shared: torch.Te
 
 def glu(gate_up: torch.Tensor, out: torch.Tensor, kind: int, limit: float, alpha: float, pairs: bool = False) -> torch.Tensor:
     """out = act(gate, up) for a gated unit's stacked product [T, 2I]: gate columns then up columns, or with ``pairs``
-    (gate, up) column by column."""
+    (gate, up) column by column.  ``kind``: ``GLU_SWISH_CLAMPED``, or a number of ``ACTIVATIONS`` other than 0:
+    out = that activation of gate, times up (computed in float, rounded once)."""
     _need_cuda(gate_up, out)
     T, I = out.shape
     _check(library().acv_glu(_p(gate_up), gate_up.stride(0), _p(out), out.stride(0), T, I, kind, limit, alpha, int(pairs),
@@ -1574,7 +1617,9 @@ def cast_rows_f32(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
-ACTIVATIONS = {"xielu": 0, "gelu_tanh": 1, "silu": 2}
+ACTIVATIONS = {"xielu": 0, "gelu_tanh": 1, "silu": 2, "gelu": 3}
+# gate activations that the tensor-core product applies in its own epilogue: name -> the epilogue's code
+GATED_EPILOGUE_ACTS = {"silu": 1}
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, kind: str, p0: float = 0.0, p1: float = 0.0) -> torch.Tensor:
@@ -1680,4 +1725,137 @@ def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out: 
         raise KernelError("rmsnorm_rows: input and output views of one shape and type with dense rows are wanted")
     _check(library().acv_rmsnorm_rows(_p(x), x.stride(0), _p(weight), float(eps), _p(out), out.stride(0), x.shape[0],
                                       x.shape[1], dtype_code(x.dtype), _stream()), "rmsnorm_rows")
+    return out
+
+
+# ----------------------------------------------------------------------------- grouped norm, a mixer's input convolution
+def add_group_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, groups: int,
+                      out: torch.Tensor, rows: torch.Tensor | None = None, delta_scale: float = 1.0) -> torch.Tensor:
+    """The float32 stream x += delta_scale * delta (in place, unless ``rows``); out = the RMS norm of x taken over each of
+    ``groups`` equal consecutive parts of the row by itself, times weight (float32 [H]); computed in float32 and rounded
+    once to out's type."""
+    _need_cuda(x, out, weight)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or (delta is not None and not delta.is_contiguous()) \
+            or weight.dtype != torch.float32:
+        raise KernelError("add_group_rmsnorm: a contiguous float32 stream, contiguous delta and output, float32 weight are wanted")
+    n = out.shape[0] if rows is not None else x.shape[0]
+    _check(library().acv_add_group_rmsnorm(_p(x), _p(delta), float(delta_scale), _p(weight), _p(out), _p(rows), n, x.shape[-1],
+                                           int(groups), eps, dtype_code(delta.dtype) if delta is not None else 0,
+                                           dtype_code(out.dtype), _stream()), "add_group_rmsnorm")
+    return out
+
+
+def input_conv(h: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor,
+               seq_of_token: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = h[t] + sum_j taps[:, j] * h[t - K + 1 + j] along each request's tokens (h float32 [T, C], taps float32
+    [C, K]); the rows before the step come from ``state`` (float32 [slots, K-1, C], oldest first), which is replaced."""
+    _need_cuda(h, taps, state, out)
+    T, C = h.shape
+    K = taps.shape[1]
+    if h.dtype != torch.float32 or taps.dtype != torch.float32 or state.dtype != torch.float32 or not h.is_contiguous() \
+            or not taps.is_contiguous() or not state.is_contiguous() or not out.is_contiguous() or taps.shape[0] != C:
+        raise KernelError("input_conv: contiguous float32 input, taps [C, K] and state are wanted")
+    _check(library().acv_input_conv(_p(h), _p(taps), _p(state), _p(slots), _p(cu_q), _p(seq_of_token), _p(out), T, C, K,
+                                    dtype_code(out.dtype), _stream()), "input_conv")
+    return out
+
+
+def add_group_rmsnorm_conv(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, groups: int,
+                           taps: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
+                           delta_scale: float = 1.0) -> torch.Tensor:
+    """``add_group_rmsnorm`` and ``input_conv`` in one launch for a step in which row r is request r's one token."""
+    _need_cuda(x, out, weight, taps, state)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or (delta is not None and
+            (not delta.is_contiguous() or delta.dtype != out.dtype)) or not taps.is_contiguous() or not state.is_contiguous():
+        raise KernelError("add_group_rmsnorm_conv: a contiguous float32 stream, and delta and output of one type, are wanted")
+    _check(library().acv_add_group_rmsnorm_conv(_p(x), _p(delta), float(delta_scale), _p(weight), _p(taps), _p(state), _p(slots),
+                                                _p(out), x.shape[0], x.shape[1], int(groups), eps, taps.shape[1],
+                                                dtype_code(out.dtype), dtype_code(out.dtype), _stream()), "add_group_rmsnorm_conv")
+    return out
+
+
+# ----------------------------------------------------------------------------- from a stacked projection to queries and pages
+def qkv_prepare(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+                q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float, cos_sin: torch.Tensor | None,
+                positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor | None,
+                k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, table_rows: torch.Tensor | None = None,
+                temp: tuple[float, int] | None = None, value_norm_eps: float | None = None,
+                shared_values: torch.Tensor | None = None, share: str | None = None, share_weight: float = 0.0) -> None:
+    """The steps between an attention layer's stacked projection [T, NH*D | NKV*D | NKV*DV] and its attention kernel, for
+    layers whose steps span more than a head; each optional, all in float, one rounding (queries in place, keys and values
+    into the pages):
+
+    ``q_weight``/``k_weight`` (float32 [NH*D], [NKV*D]): RMS norm over the whole of q and the whole of k; ``cos_sin``: partial
+    rotate-half rotation by table; ``temp`` = (coef, every): q *= 1 + coef ln(floor((p + 1) / every) + 1);
+    ``value_norm_eps``: every value head to unit RMS; ``share`` "source": the values are left in ``shared_values``
+    (float32 [T, NKV*DV]); "mix": v <- (1 - share_weight) v + share_weight * shared_values."""
+    _need_cuda(qkv)
+    T = qkv.shape[0]
+    rot = cos_sin.shape[1] if cos_sin is not None else 0
+    rows = cos_sin.shape[0] if cos_sin is not None else 0
+    page = k_pages.shape[2] if k_pages is not None else 1
+    n_pages = k_pages.shape[0] if k_pages is not None else 0
+    bts = block_table.stride(0) if block_table is not None else 0
+    mode = {None: 0, "source": 1, "mix": 2}[share]
+    if mode and (shared_values is None or shared_values.dtype != torch.float32 or not shared_values.is_contiguous()
+                 or shared_values.shape != (T, num_kv_heads * value_dim)):
+        raise KernelError("qkv_prepare: shared values are float32 [tokens, kv heads * value dim]")
+    if qkv.stride(1) != 1 or qkv.shape[1] < (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim:
+        raise KernelError("qkv_prepare: the projection's rows are [q | k | v], dense")
+    coef, every = temp if temp else (0.0, 0)
+    _check(library().acv_qkv_prepare(
+        _p(qkv), qkv.stride(0), T, num_heads, num_kv_heads, head_dim, value_dim, _p(q_weight), _p(k_weight), eps, _p(cos_sin),
+        rot, rows, float(coef), int(every), 1 if value_norm_eps is not None else 0, float(value_norm_eps or 0.0),
+        _p(shared_values), mode, float(share_weight), _p(positions), _p(seq_of_token), _p(block_table), bts, _p(table_rows),
+        _p(k_pages), _p(v_pages), page, n_pages, dtype_code(qkv.dtype), _stream()), "qkv_prepare")
+
+
+# ----------------------------------------------------------------------------- a recurrence with decays of the token's own
+def token_shift_multi(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor,
+                      seq_of_token: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[s, t] = h[t] + (h[t-1] - h[t]) * mu[s] along each request's tokens (mu float32 [S, C]); the row before the step
+    comes from ``state`` (float32 [slots, C]), which the step's last row replaces.  Mixed in float, rounded once."""
+    _need_cuda(h, mu, state, out)
+    T, C = h.shape
+    S = mu.shape[0]
+    if mu.dtype != torch.float32 or state.dtype != torch.float32 or not h.is_contiguous() or not mu.is_contiguous() \
+            or not state.is_contiguous() or not out.is_contiguous() or out.shape != (S, T, C) or out.dtype != h.dtype:
+        raise KernelError("token_shift_multi: contiguous h [T, C], float32 mu [S, C] and state, out [S, T, C] of h's type are wanted")
+    _check(library().acv_token_shift_multi(_p(h), _p(mu), _p(state), _p(slots), _p(cu_q), _p(seq_of_token), _p(out), T, C, S,
+                                           dtype_code(h.dtype), _stream()), "token_shift_multi")
+    return out
+
+
+def wkv_decay(a: torch.Tensor, w2_t: torch.Tensor, w0: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, c] = exp(-exp(w0[c] + sum_j w2_t[j, c] tanh(a[t, j]))): all float32; a [T, L], w2_t [L, C], out [T, C]."""
+    _need_cuda(a, w2_t, w0, out)
+    T, L = a.shape
+    C = w2_t.shape[1]
+    if any(t.dtype != torch.float32 for t in (a, w2_t, w0, out)) or a.stride(1) != 1 or not w2_t.is_contiguous() \
+            or not out.is_contiguous() or w2_t.shape[0] != L or out.shape != (T, C):
+        raise KernelError("wkv_decay: float32 a [T, L], w2_t [L, C], w0 [C], out [T, C] are wanted")
+    _check(library().acv_wkv_decay(_p(a), a.stride(0), _p(w2_t), _p(w0), _p(out), T, C, L, _stream()), "wkv_decay")
+    return out
+
+
+def wkv(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor, state: torch.Tensor,
+        slots: torch.Tensor, cu_q: torch.Tensor, num_seqs: int, out: torch.Tensor, num_heads: int, dim: int, value_dim: int,
+        work: dict | None = None) -> torch.Tensor:
+    """o_t = (S + diag(u) k_t v_t^T)^T r_t, then S = diag(w_t) S + k_t v_t^T, along each request's tokens, per head.
+    r, k ([T, H*dim]) and v ([T, H*value_dim]): one type and row stride; w float32 [T, H*dim] (the decays); u float32
+    [H*dim]; state float32 [slots, H, dim, value_dim]; out float32 [T, H*value_dim].  ``work``: the step's segments
+    (``segment_work``); default: every request's portion is one item."""
+    _need_cuda(r, k, v, w, u, state, out)
+    if not (r.stride(0) == k.stride(0) == v.stride(0)) or r.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1 \
+            or not (r.dtype == k.dtype == v.dtype):
+        raise KernelError("wkv: r, k and v of one type with one row stride and dense rows are wanted")
+    if out.dtype != torch.float32 or state.dtype != torch.float32 or not state.is_contiguous() or out.stride(1) != 1 \
+            or w.dtype != torch.float32 or not w.is_contiguous() or u.dtype != torch.float32 or not u.is_contiguous():
+        raise KernelError("wkv: float32 decays, bonus, state and output are wanted")
+    seg_seq, seg_idx, seg_len, n_items, summaries = _segments(work, num_seqs)
+    seg = torch.empty((n_items, num_heads, dim, value_dim), device=r.device, dtype=torch.float32) if summaries else None
+    seg_decay = torch.empty((n_items, num_heads, dim), device=r.device, dtype=torch.float32) if summaries else None
+    _check(library().acv_wkv(_p(r), _p(k), _p(v), r.stride(0), _p(w), _p(u), _p(state), _p(slots), _p(cu_q), _p(seg_seq),
+                             _p(seg_idx), seg_len, _p(seg), _p(seg_decay), 1 if summaries else 0, _p(out), out.stride(0),
+                             n_items, num_heads, dim, value_dim, dtype_code(r.dtype), _stream()), "wkv")
     return out

@@ -13,6 +13,7 @@ from . import qwen3  # noqa: F401  (registers Qwen3ForCausalLM)
 from . import zotonex  # noqa: F401  (registers Zotonex)
 from . import redudra  # noqa: F401  (registers Redudra)
 from . import nizedra  # noqa: F401  (registers Nizedra)
+from . import vadelix  # noqa: F401  (registers Vadelix)
 from .decoder import DecoderModel
 
 __all__ = ["DecoderModel", "build_from_folder", "build_random", "needs_of_plan", "plan_of_folder"]

@@ -28,13 +28,22 @@ class PreNormBlock:
       ``token_shift``: the name (behind the layer's prefix) of a vector mu of the stream's width.  What the mixer reads is
         then h'[t] = h[t] + (h[t-1] - h[t]) * mu, h the first norm's output and h[t-1] the same of the request's previous
         token (zeros before its first): the layer keeps one row of h for every request, in a state slot beside what its
-        mixer keeps, and the mix is made in 32-bit before h' is rounded to the parts' element type."""
+        mixer keeps, and the mix is made in 32-bit before h' is rounded to the parts' element type.
+      ``input_conv``: {"tensor": name behind the layer's prefix, "taps": K}: what the mixer reads is h + conv(h), h the
+        first norm's output and conv a causal convolution over time on every channel by itself, conv(h)[t] =
+        sum_j w[:, j] h[t - K + 1 + j] (w: [width, K], zeros before the request's first token).  The layer keeps the last
+        K - 1 rows of h for every request in a state slot beside what its mixer keeps; norm output, convolution and kept
+        rows are 32-bit, the sum is rounded once to the parts' element type."""
 
     def __init__(self, spec: LayerSpec, hidden_size: int) -> None:
         self.hidden_size = hidden_size
         self.residual_mult = float(spec.options.get("residual_mult", 1.0))
         self.token_shift = spec.options.get("token_shift")
         self.shift_mu = None
+        self.input_conv = spec.options.get("input_conv")
+        self.conv_taps = None
+        if self.input_conv is not None and self.token_shift is not None:
+            raise ValueError("the pre-norm block takes a token shift or an input convolution, not both")
         self.prefix = spec.prefix
         self.pre_mixer, self.pre_ff = spec.norm_prefixes
         self.input_norm = build("norm", spec.norm, hidden_size)
@@ -59,6 +68,8 @@ class PreNormBlock:
             needs.update(self.feed_forward.tensor_needs())
         if self.token_shift is not None:
             needs[self.token_shift] = TensorNeed((self.hidden_size,))
+        if self.input_conv is not None:
+            needs[self.input_conv["tensor"]] = TensorNeed((self.hidden_size, int(self.input_conv["taps"])))
         return needs
 
     def load(self, tensors, rt: Runtime) -> None:
@@ -71,9 +82,15 @@ class PreNormBlock:
             self.feed_forward.load(tensors, rt)
         if self.token_shift is not None:
             self.shift_mu = tensors[self.token_shift].to(device=rt.device, dtype=torch.float32).contiguous()
+        if self.input_conv is not None:
+            self.conv_taps = tensors[self.input_conv["tensor"]].to(device=rt.device, dtype=torch.float32).contiguous()
 
     def cache_need(self):
         need = self.mixer.cache_need()
+        if self.input_conv is not None:
+            # (a convolution of one tap keeps nothing; its slot of one row is never touched)
+            conv = StateNeed((max(int(self.input_conv["taps"]) - 1, 1), self.hidden_size), "float32")
+            return {"mixer": need, "conv": conv} if need is not None else {"conv": conv}
         if self.token_shift is None:
             return need
         shift = StateNeed((self.hidden_size,), "float32")
@@ -93,6 +110,19 @@ class PreNormBlock:
         normed = self.input_norm.forward(x, delta, out_dtype=torch.float32, **scale)
         out = torch.empty(normed.shape, device=x.device, dtype=out_dtype)
         return ops.token_shift(normed, self.shift_mu, shift_view.state, slots, ctx.cu_q, ctx.seq_of_token, out)
+
+    def _normed_conv(self, x, delta, ctx, conv_view: CacheView, kw: dict, scale: dict):
+        """h + conv(h), h the first norm's output, in the parts' element type."""
+        slots = ctx.state_slots[conv_view.group]
+        out = torch.empty((x.shape[0], x.shape[1]), device=x.device, dtype=kw.get("out_dtype", x.dtype))
+        n = self.input_norm
+        if ctx.max_q_len == 1 and ctx.num_tokens == ctx.num_seqs and hasattr(n, "groups") and x.dtype == torch.float32 \
+                and (delta is None or delta.dtype == out.dtype):
+            # every request brings one token: sum, norm, convolution and the state's shift in one launch
+            return ops.add_group_rmsnorm_conv(x, delta, n.weight, n.eps, n.groups, self.conv_taps, conv_view.state, slots, out,
+                                              scale.get("delta_scale", 1.0))
+        normed = n.forward(x, delta, out_dtype=torch.float32, **scale)
+        return ops.input_conv(normed, self.conv_taps, conv_view.state, slots, ctx.cu_q, ctx.seq_of_token, out)
 
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in (self.input_norm, self.post_norm, self.mixer, self.feed_forward) if p is not None)
@@ -145,6 +175,9 @@ class PreNormBlock:
         scale = {"delta_scale": self.residual_mult} if self.residual_mult != 1.0 else {}
         if self.token_shift is not None:
             h = self._normed_shifted(x, delta, ctx, cache.parts["shift"], kw, scale)
+            cache = cache.parts.get("mixer")
+        elif self.input_conv is not None:
+            h = self._normed_conv(x, delta, ctx, cache.parts["conv"], kw, scale)
             cache = cache.parts.get("mixer")
         else:
             h = self.input_norm.forward(x, delta, **kw, **scale)

@@ -19,9 +19,14 @@ class SwiGLU(FeedForward):
     (acvram/engine/attention.py:705-783)."""
 
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "mlp.", bias: bool | None = None,
-                 names: dict | None = None) -> None:
+                 names: dict | None = None, activation: str = "silu") -> None:
         """``bias``: True, the three projections have biases; False, none; None, those that the file holds.
-        ``names``: the tensors' names behind ``prefix``, {"gate": w, "gate.bias": b, "up": ..., "down": ...}."""
+        ``names``: the tensors' names behind ``prefix``, {"gate": w, "gate.bias": b, "up": ..., "down": ...}.
+        ``activation``: what the gate passes through, "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))),
+        computed in float."""
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated feed-forward: no activation '{activation}' (silu and gelu_tanh are built)")
+        self.activation = activation
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.prefix = prefix
         self.bias = bias
@@ -60,6 +65,7 @@ class SwiGLU(FeedForward):
         # stacked product's output [T, 2I] is then never written.  Otherwise: stacked product, then the kernel.
         # (biases of gate and up are interleaved the same way and join the accumulators in that epilogue)
         self.fused = rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
+        self.fused_act = ops.GATED_EPILOGUE_ACTS.get(self.activation)
         if self.fused:
             pair_bias = None
             if gate_b is not None or up_b is not None:
@@ -73,20 +79,24 @@ class SwiGLU(FeedForward):
 
     def decode_layer_spec(self):
         """What the fused decode-layer kernel needs of this feed-forward: gate and up rows interleaved, no biases."""
-        if not self.fused or self.down.bias is not None or self.gate_up.bias is not None:
+        if not self.fused or self.down.bias is not None or self.gate_up.bias is not None or self.activation != "silu":
             return None
         return {"intermediate_size": self.intermediate_size, "w_gate_up_pairs": self.gate_up.weight, "w_down": self.down.weight}
 
     def forward(self, h, ctx):
-        if self.fused and h.shape[0] and ops.gemm_tc_takes(h, self.gate_up.weight):
+        if self.fused and self.fused_act is not None and h.shape[0] and ops.gemm_tc_takes(h, self.gate_up.weight):
             act = torch.empty((h.shape[0], self.intermediate_size), device=h.device, dtype=h.dtype)
-            ops.linear_bf16_swiglu(h, self.gate_up.weight, act, static_weights=True, bias=self.gate_up.bias)
+            ops.linear_bf16_swiglu(h, self.gate_up.weight, act, static_weights=True, bias=self.gate_up.bias,
+                                   **({"act": self.fused_act} if self.activation != "silu" else {}))
             return self.down(act)
+        act = torch.empty((h.shape[0], self.intermediate_size), device=h.device, dtype=h.dtype)
+        if self.activation != "silu":
+            # the gate's activation in float on the stacked product's output, rounded once
+            return self.down(ops.glu(self.gate_up(h), act, ops.ACTIVATIONS[self.activation], 0.0, 0.0, pairs=self.fused))
         if self.fused:      # an input the tensor-core kernel does not take: undo the interleaving for this call
             gu = self.gate_up(h).view(h.shape[0], self.intermediate_size, 2).transpose(1, 2).reshape(h.shape[0], -1)
         else:
             gu = self.gate_up(h)
-        act = torch.empty((h.shape[0], self.intermediate_size), device=h.device, dtype=h.dtype)
         ops.swiglu(gu, act)
         return self.down(act)
 
@@ -106,19 +116,41 @@ class RoutedExperts(FeedForward):
     (``shared_ff`` > 0: the same unit with sizes and a limit of its own) runs for every token and is added times
     sigmoid(<w_sg, h>), one number per token, computed in 32-bit with the router.
 
+    Variants: ``expert_form`` "plain": an expert (and the shared one) has no gate, W_down act(W_up x) with ``activation`` a
+    name of ``ops.ACTIVATIONS`` ("gelu": the exact one, with erf), no clamps; ``groups`` = (count, keep): the experts stand in
+    ``count`` equal groups of neighbours, a group is worth its best score, and only experts of the ``keep`` best groups can
+    be chosen; ``renorm_eps`` joins the sum that the chosen scores are divided by; ``shared_gate`` False: the shared
+    expert's output is added as it is (no tensor shared.sg).
+
     The step is the same launches whatever the routing is (rows grouped by expert on the device, tiles that belong
     to no expert return at once), so it runs inside a captured graph.  Tensors behind ``prefix``: router, e<i>.gate,
     e<i>.up, e<i>.down, shared.gate, shared.up, shared.down, shared.sg."""
 
     def __init__(self, hidden_size: int, experts: int, top: int, expert_ff: int, expert_limit: float, shared_ff: int = 0,
                  shared_limit: float = 0.0, alpha: float = 1.702, scoring: str = "sigmoid", renormalize: bool = False,
-                 weight_on: str = "input", prefix: str = "mlp.") -> None:
+                 weight_on: str = "input", prefix: str = "mlp.", expert_form: str = "glu", activation: str | None = None,
+                 groups: tuple | None = None, renorm_eps: float = 0.0, shared_gate: bool = True) -> None:
         if scoring not in ("sigmoid", "softmax"):
             raise ValueError(f"router scoring '{scoring}' is not built (sigmoid and softmax are)")
         if weight_on not in ("input", "output"):
             raise ValueError(f"weight_on must be 'input' or 'output', got '{weight_on}'")
         if not 1 <= top <= experts:
             raise ValueError(f"top {top} must lie in 1..{experts}")
+        if expert_form not in ("glu", "plain"):
+            raise ValueError(f"expert_form is 'glu' or 'plain', got '{expert_form}'")
+        self.plain = expert_form == "plain"
+        if self.plain and (activation not in ops.ACTIVATIONS or ops.ACTIVATIONS[activation] == 0):
+            raise ValueError(f"plain experts: no activation '{activation}'")
+        if self.plain and weight_on != "output":
+            raise ValueError("plain experts are not linear in their input: the weight goes on the output")
+        self.activation = activation
+        self.groups = (int(groups[0]), int(groups[1])) if groups else None
+        if self.groups is not None:
+            count, keep = self.groups
+            if count < 1 or experts % count or not 1 <= keep <= count or top > keep * (experts // count) or count > 32:
+                raise ValueError(f"{experts} experts in {count} groups of which {keep} are kept cannot give {top} choices")
+        self.renorm_eps = float(renorm_eps)
+        self.shared_gated = bool(shared_gate)
         self.hidden_size, self.experts, self.top = hidden_size, experts, top
         self.expert_ff, self.expert_limit = expert_ff, float(expert_limit)
         self.shared_ff, self.shared_limit = shared_ff, float(shared_limit)
@@ -129,13 +161,17 @@ class RoutedExperts(FeedForward):
         H, F, p = self.hidden_size, self.expert_ff, self.prefix
         needs = {p + "router": TensorNeed((self.experts, H))}
         for e in range(self.experts):
-            needs[f"{p}e{e}.gate"] = TensorNeed((F, H))
+            if not self.plain:
+                needs[f"{p}e{e}.gate"] = TensorNeed((F, H))
             needs[f"{p}e{e}.up"] = TensorNeed((F, H))
             needs[f"{p}e{e}.down"] = TensorNeed((H, F))
         if self.shared_ff:
             S = self.shared_ff
-            needs.update({p + "shared.gate": TensorNeed((S, H)), p + "shared.up": TensorNeed((S, H)),
-                          p + "shared.down": TensorNeed((H, S)), p + "shared.sg": TensorNeed((1, H))})
+            needs.update({p + "shared.up": TensorNeed((S, H)), p + "shared.down": TensorNeed((H, S))})
+            if not self.plain:
+                needs[p + "shared.gate"] = TensorNeed((S, H))
+            if self.shared_gated:
+                needs[p + "shared.sg"] = TensorNeed((1, H))
         return needs
 
     def load(self, tensors, rt: Runtime) -> None:
@@ -146,25 +182,29 @@ class RoutedExperts(FeedForward):
         # [E, 2F, H]: an expert's gate and up rows; [E, H, F].  bfloat16 with rows of 16-byte alignment: (gate, up) row by
         # row, the layout that the tcgen05 product's epilogue wants (the other kernels read either); else all gate
         # rows, then all up rows
-        self.pairs = rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.expert_ff % 8 == 0
-        self.gate_up = torch.stack([
+        self.pairs = rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.expert_ff % 8 == 0 and not self.plain
+        self.gate_up = torch.stack([w(f"e{e}.up") for e in range(self.experts)]).contiguous() if self.plain else torch.stack([
             torch.stack([w(f"e{e}.gate"), w(f"e{e}.up")], dim=1).reshape(2 * self.expert_ff, self.hidden_size) if self.pairs
             else torch.cat([w(f"e{e}.gate"), w(f"e{e}.up")], dim=0) for e in range(self.experts)]).contiguous()
         self.down = torch.stack([w(f"e{e}.down") for e in range(self.experts)]).contiguous()
         self.shared_gate_up = self.shared_down = self.shared_gate = None
-        if self.shared_ff:
+        if self.shared_ff and self.plain:
+            self.shared_pairs = False
+            self.shared_gate_up, self.shared_down = Linear(w("shared.up")), Linear(w("shared.down"))
+        elif self.shared_ff:
             # with rows of 16-byte alignment in bfloat16: (gate, up) row by row, so that a step of many tokens applies the
             # activation in the product's epilogue
             self.shared_pairs = rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.shared_ff % 8 == 0
             self.shared_gate_up = (Linear(torch.stack([w("shared.gate"), w("shared.up")], dim=1).reshape(2 * self.shared_ff, self.hidden_size))
                                    if self.shared_pairs else Linear.stacked([w("shared.gate"), w("shared.up")]))
             self.shared_down = Linear(w("shared.down"))
+        if self.shared_ff and self.shared_gated:
             self.shared_gate = tensors[p + "shared.sg"].to(device=rt.device, dtype=torch.float32).reshape(-1).contiguous()
         # The router's logits (and the shared gate's) as one matrix product with 32-bit accumulation: in a float32 run
         # the CUDA-core product; in a bfloat16 run the tensor-core product with float output, which is the same 32-bit
         # arithmetic when the weights are bfloat16 values anyway (products of two bfloat16 numbers are exact in float).
         # Weights that bfloat16 cannot hold keep the router kernel that reads them as float.
-        rows = [self.router] + ([self.shared_gate[None, :]] if self.shared_ff else [])
+        rows = [self.router] + ([self.shared_gate[None, :]] if self.shared_gate is not None else [])
         stacked = torch.cat(rows + [torch.zeros((-len(torch.cat(rows)) % 8, self.hidden_size), device=rt.device)])
         self.router_linear = None
         if rt.dtype == torch.float32 or bool((stacked.to(torch.bfloat16).float() == stacked).all()):
@@ -176,7 +216,8 @@ class RoutedExperts(FeedForward):
         is ``active_weight_bytes``)."""
         n = self.router.numel() * 4 + (self.gate_up.numel() + self.down.numel()) * self.gate_up.element_size()
         if self.shared_ff:
-            n += self.shared_gate_up.weight_bytes() + self.shared_down.weight_bytes() + self.shared_gate.numel() * 4
+            n += self.shared_gate_up.weight_bytes() + self.shared_down.weight_bytes() + \
+                (self.shared_gate.numel() * 4 if self.shared_gate is not None else 0)
         return n
 
     def step_weight_bytes(self, num_tokens: int) -> int:
@@ -186,13 +227,15 @@ class RoutedExperts(FeedForward):
         per = (self.gate_up.numel() + self.down.numel()) // self.experts * self.gate_up.element_size()
         n = self.router.numel() * 4 + int(active * per)
         if self.shared_ff:
-            n += self.shared_gate_up.weight_bytes() + self.shared_down.weight_bytes() + self.shared_gate.numel() * 4
+            n += self.shared_gate_up.weight_bytes() + self.shared_down.weight_bytes() + \
+                (self.shared_gate.numel() * 4 if self.shared_gate is not None else 0)
         return n
 
     def flops(self, num_tokens: int) -> float:
         H = self.hidden_size
-        n = 2.0 * num_tokens * self.experts * H + 6.0 * num_tokens * self.top * self.expert_ff * H
-        return n + (6.0 * num_tokens * self.shared_ff * H if self.shared_ff else 0.0)
+        per = 4.0 if self.plain else 6.0        # an expert is two products, or three with a gate
+        n = 2.0 * num_tokens * self.experts * H + per * num_tokens * self.top * self.expert_ff * H
+        return n + (per * num_tokens * self.shared_ff * H if self.shared_ff else 0.0)
 
     def forward(self, h, ctx):
         T, H = h.shape
@@ -202,16 +245,18 @@ class RoutedExperts(FeedForward):
         tiles = ops.moe_max_tiles(rows, E)
         ids = torch.empty(rows, device=dev, dtype=torch.int32)
         weights = torch.empty(rows, device=dev, dtype=torch.float32)
-        gate = torch.empty(T, device=dev, dtype=torch.float32) if self.shared_ff else None
+        gate = torch.empty(T, device=dev, dtype=torch.float32) if self.shared_gate is not None else None
+        route = {"groups": self.groups, "renorm_eps": self.renorm_eps}
         if self.router_linear is not None:
             # many tokens against a few dozen router rows: one column of tiles, so the reduction is split eight ways
             # to put more than a ninth of the SMs to work
             plan = (0, 128, 8, 4, 0) if h.dtype == torch.bfloat16 and T >= 512 and H >= 2048 and self.router_linear.out_features <= 128 else None
             logits = self.router_linear(h, out_dtype=torch.float32, plan=plan)
             ops.moe_route(h, None, None, top, self.scoring == "softmax", self.renormalize, ids, weights, gate, logits=logits,
-                          experts=E)
+                          experts=E, **route)
         else:
-            ops.moe_route(h, self.router, self.shared_gate, top, self.scoring == "softmax", self.renormalize, ids, weights, gate)
+            ops.moe_route(h, self.router, self.shared_gate, top, self.scoring == "softmax", self.renormalize, ids, weights, gate,
+                          **route)
         place = torch.empty(rows, device=dev, dtype=torch.int32)
         w_in = weights if self.weight_on == "input" else None
         w_out = weights if self.weight_on == "output" else None
@@ -236,11 +281,16 @@ class RoutedExperts(FeedForward):
             tile_expert = torch.empty(tiles, device=dev, dtype=torch.int32)
             ops.moe_group(ids, E, grouped, place, tile_expert)
             act = torch.empty((tiles * ops.MOE_TILE, F), device=dev, dtype=h.dtype)
-            ops.moe_experts_up(h, self.gate_up, act, grouped, tile_expert, w_in, top, self.expert_limit, self.alpha, self.pairs)
+            ops.moe_experts_up(h, self.gate_up, act, grouped, tile_expert, w_in, top, self.expert_limit, self.alpha, self.pairs,
+                               plain_act=self.activation if self.plain else None)
             parts = torch.empty((tiles * ops.MOE_TILE, H), device=dev, dtype=torch.float32)
             ops.moe_experts_down(act, self.down, parts, grouped, tile_expert, w_out, top)
         shared = None
-        if self.shared_ff:
+        if self.shared_ff and self.plain:
+            sact = self.shared_gate_up(h)
+            ops.activation(sact, sact, self.activation)
+            shared = self.shared_down(sact)
+        elif self.shared_ff:
             sact = torch.empty((T, self.shared_ff), device=dev, dtype=h.dtype)
             if self.shared_pairs and ops.linear_bf16_glu_takes(h, self.shared_gate_up.weight):
                 ops.linear_bf16_glu(h, self.shared_gate_up.weight, sact, self.shared_limit, self.alpha)

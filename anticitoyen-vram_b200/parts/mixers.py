@@ -38,7 +38,18 @@ class Attention(Mixer):
                                                     the distance from which every key reads the last row; rows/2 single
                                                     distances first, the rest spread evenly over ln(distance)
         m_h = sum_g talk[h][g] s_g                  "talk": tensor [heads, heads]; the softmax is taken over m_h
-    (tensor names behind ``prefix``).  Such a layer runs ``ops.attention_mixed``."""
+    (tensor names behind ``prefix``).  Such a layer runs ``ops.attention_mixed``.
+
+    Steps that span more than a head, each optional, all 32-bit (``ops.qkv_prepare`` between projection and attention):
+    ``qk_norm_scope`` "all": one root mean square over the whole of q (and one over the whole of k) with a weight for
+    every element (names["q_norm"], names["k_norm"]) instead of a norm per head; ``value_norm_eps``: every value head is
+    divided by its root mean square before it is kept; ``q_temp`` = (coef, every): the query at position p is multiplied
+    by 1 + coef ln(floor((p + 1) / every) + 1); ``value_share`` = {"key", "role", "tensor"}: the layer with role "source"
+    leaves its values (as it keeps them) under ``key`` for the later layers of the step, a layer with role "mix" keeps
+    (1 - lambda) v + lambda v_source, lambda its own number in ``tensor``.
+    ``sink``: the softmax's denominator also holds exp(sink_h), a score with no key and no value: a tensor's name (one
+    learned number per query head) or a constant for all heads.  ``slope_rate`` r: slope_h (i - j) is taken off the score
+    of query i and key j, slope_h = 2^(-r (h + 1) / heads)."""
 
     ROLES = ("q", "k", "v", "o")
 
@@ -46,9 +57,30 @@ class Attention(Mixer):
                  qk_norm_eps: float | None = None, scale: float | None = None, window: int = 0,
                  prefix: str = "self_attn.", bias: bool | None = None, value_dim: int | None = None, keep_first: int = 0,
                  names: dict | None = None, out_scale: float = 1.0, qk_norm_weights: bool = True,
-                 score: dict | None = None) -> None:
+                 score: dict | None = None, qk_norm_scope: str = "head", value_norm_eps: float | None = None,
+                 q_temp: tuple | None = None, value_share: dict | None = None, sink: str | float | None = None,
+                 slope_rate: float | None = None) -> None:
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
+        if qk_norm_scope not in ("head", "all"):
+            raise ValueError(f"attention: qk_norm_scope is 'head' or 'all', got {qk_norm_scope!r}")
+        if value_share is not None and (value_share.get("role") not in ("source", "mix") or "key" not in value_share
+                                        or (value_share["role"] == "mix" and "tensor" not in value_share)):
+            raise ValueError("attention: value_share is {'key', 'role': 'source' | 'mix', 'tensor' (of a 'mix')}")
+        self.qk_norm_scope = qk_norm_scope
+        self.value_norm_eps = float(value_norm_eps) if value_norm_eps is not None else None
+        self.q_temp = (float(q_temp[0]), int(q_temp[1])) if q_temp else None
+        self.value_share = dict(value_share) if value_share else None
+        self.sink = sink
+        self.slope_rate = float(slope_rate) if slope_rate is not None else None
+        self.sinks = self.slopes = None
+        self.share_weight = 0.0
+        # steps that one warp per (token, head) cannot make: they run in a kernel that holds a token's whole projection
+        self.wide = qk_norm_scope == "all" and qk_norm_eps is not None or self.value_norm_eps is not None \
+            or self.q_temp is not None or self.value_share is not None
+        if (self.wide or sink is not None or slope_rate is not None) and (score or keep_first or out_scale != 1.0):
+            raise ValueError("attention: sinks, slopes and the steps over whole projections are not built beside score steps, "
+                             "kept first tokens or an output factor")
         self.hidden_size = hidden_size
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.qk_norm_weights = bool(qk_norm_weights)
@@ -104,8 +136,14 @@ class Attention(Mixer):
             if self.bias is not False and role + ".bias" in self.names:
                 needs[self.prefix + self.names[role + ".bias"]] = TensorNeed((n_out,), "bias", optional=self.bias is None)
         if self.qk_norm_eps is not None and self.qk_norm_weights:
-            needs[self.prefix + "q_norm.weight"] = TensorNeed((self.head_dim,), "norm")
-            needs[self.prefix + "k_norm.weight"] = TensorNeed((self.head_dim,), "norm")
+            whole = self.qk_norm_scope == "all"
+            needs[self.prefix + self.names.get("q_norm", "q_norm.weight")] = TensorNeed((self.q_size if whole else self.head_dim,), "norm")
+            needs[self.prefix + self.names.get("k_norm", "k_norm.weight")] = TensorNeed((self.kv_size if whole else self.head_dim,), "norm")
+        if isinstance(self.sink, str):
+            needs[self.prefix + self.sink] = TensorNeed((self.num_heads,), "norm")
+        if self.value_share is not None and "tensor" in self.value_share:
+            # (the source layer's number is read by nobody; a file may carry it all the same)
+            needs[self.prefix + self.value_share["tensor"]] = TensorNeed((), "norm", optional=self.value_share["role"] == "source")
         if self.score is not None:
             NH = self.num_heads
             for key, shape, role in (("temp", (NH,), "norm"), ("rel", (-1, NH), "matrix"), ("talk", (NH, NH), "matrix")):
@@ -127,9 +165,22 @@ class Attention(Mixer):
         self.q_norm = self.k_norm = None
         f = lambda n: tensors[n].to(device=rt.device, dtype=torch.float32).contiguous()
         if self.qk_norm_eps is not None and self.qk_norm_weights:
-            self.q_norm, self.k_norm = f(self.prefix + "q_norm.weight"), f(self.prefix + "k_norm.weight")
+            self.q_norm = f(self.prefix + self.names.get("q_norm", "q_norm.weight"))
+            self.k_norm = f(self.prefix + self.names.get("k_norm", "k_norm.weight"))
+        elif self.qk_norm_eps is not None and self.qk_norm_scope == "all":
+            self.q_norm = torch.ones(self.q_size, device=rt.device, dtype=torch.float32)
+            self.k_norm = torch.ones(self.kv_size, device=rt.device, dtype=torch.float32)
         elif self.qk_norm_eps is not None:
             self.q_norm = self.k_norm = torch.ones(self.head_dim, device=rt.device, dtype=torch.float32)
+        if isinstance(self.sink, str):
+            self.sinks = f(self.prefix + self.sink)
+        elif self.sink is not None:
+            self.sinks = torch.full((self.num_heads,), float(self.sink), device=rt.device, dtype=torch.float32)
+        if self.slope_rate is not None:
+            steps = torch.arange(1, self.num_heads + 1, dtype=torch.float64)
+            self.slopes = torch.exp2(-self.slope_rate * steps / self.num_heads).to(device=rt.device, dtype=torch.float32)
+        if self.value_share is not None and self.value_share["role"] == "mix":
+            self.share_weight = float(tensors[self.prefix + self.value_share["tensor"]].to(torch.float64))
         if self.score is not None:
             sc = self.score
             self.temp = f(self.prefix + sc["temp"]) if "temp" in sc else None
@@ -154,7 +205,7 @@ class Attention(Mixer):
 
     # ---- cost of a step
     def extra_weight_bytes(self) -> int:
-        return sum(t.numel() * 4 for t in (self.q_norm, self.k_norm, self.temp, self.rel, self.talk) if t is not None)
+        return sum(t.numel() * 4 for t in (self.q_norm, self.k_norm, self.temp, self.rel, self.talk, self.sinks) if t is not None)
 
     def _attend(self, qkv, out, ctx, cache: CacheView, table) -> None:
         """From normed, positioned queries (the first columns of ``qkv``) and the pages to the heads' outputs."""
@@ -166,7 +217,35 @@ class Attention(Mixer):
                                 last_row=self.rel_last, talk=self.talk, ctx=ctx, work=ctx.work.get(self.metadata_key))
             return
         ops.attention(qkv, out, cache.k_pages, cache.v_pages, ctx, table, NH, NKV, D, self.scale, self.window,
-                      work=ctx.work[self.metadata_key], value_dim=DV, keep_first=self.keep_first)
+                      work=ctx.work[self.metadata_key], value_dim=DV, keep_first=self.keep_first, sinks=self.sinks,
+                      slopes=self.slopes)
+
+    def _prepare(self, qkv, ctx, table, rows, kp, vp) -> None:
+        """The steps over a token's whole projection, rotation and append in one launch."""
+        share = self.value_share
+        shared_values = None
+        if share is not None:
+            T = qkv.shape[0]
+            if share["role"] == "source":
+                shared_values = ctx.shared[share["key"]] = torch.empty((T, self.v_size), device=qkv.device, dtype=torch.float32)
+            else:
+                shared_values = ctx.shared.get(share["key"])
+                if shared_values is None or shared_values.shape != (T, self.v_size):
+                    raise ValueError(f"attention: no layer before this one left values of this size under '{share['key']}'")
+        whole = self.qk_norm_scope == "all" and self.qk_norm_eps is not None
+        if self.q_norm is not None and not whole:
+            # a norm per head beside steps over the whole projection: the per-head kernel first (no rotation, no append)
+            ops.qk_norm_rope_append(qkv, self.num_heads, self.num_kv_heads, self.head_dim, self.q_norm, self.k_norm,
+                                    self.qk_norm_eps, None, ctx.positions, ctx.seq_of_token, None, None, None,
+                                    value_dim=self.value_dim if self.value_dim != self.head_dim else 0)
+        rotary = self.position.rotary_table()
+        if rotary is None and not isinstance(self.position, NoPosition):
+            raise ValueError("attention: the steps over whole projections take rotary positions by table, or none")
+        ops.qkv_prepare(qkv, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim,
+                        self.q_norm if whole else None, self.k_norm if whole else None, self.qk_norm_eps or 0.0, rotary,
+                        ctx.positions, ctx.seq_of_token, table if kp is not None else None, kp, vp, table_rows=rows,
+                        temp=self.q_temp, value_norm_eps=self.value_norm_eps, shared_values=shared_values,
+                        share=share["role"] if share else None, share_weight=self.share_weight)
 
     def weight_bytes(self) -> int:
         return self.qkv.weight_bytes() + self.o.weight_bytes() + self.extra_weight_bytes()
@@ -199,7 +278,9 @@ class Attention(Mixer):
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
         rotary = self.position.rotary_table()
         extra = {"value_dim": DV, "v_scale": self.out_scale} if (DV != D or self.out_scale != 1.0) else {}
-        if rotary is not None:
+        if self.wide:
+            self._prepare(qkv, ctx, table, rows, kp, vp)
+        elif rotary is not None:
             ops.qk_norm_rope_append(qkv, NH, NKV, D, self.q_norm, self.k_norm, eps, rotary, ctx.positions,
                                     ctx.seq_of_token, table if kp is not None else None, kp, vp, table_rows=rows, **extra)
         elif isinstance(self.position, NoPosition):
@@ -220,7 +301,8 @@ class Attention(Mixer):
 
     def forward(self, h, ctx, cache: CacheView):
         NH, NKV, D = self.num_heads, self.num_kv_heads, self.head_dim
-        if self.value_dim != D or self.out_scale != 1.0 or self.score is not None or isinstance(self.position, NoPosition):
+        if self.value_dim != D or self.out_scale != 1.0 or self.score is not None or isinstance(self.position, NoPosition) \
+                or self.wide or self.sinks is not None or self.slopes is not None:
             qkv = self.qkv(h)
             out = torch.empty((qkv.shape[0], self.inner_size), device=h.device, dtype=h.dtype)
             self.mix(qkv, ctx, cache, out)

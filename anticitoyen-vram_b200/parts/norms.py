@@ -16,9 +16,14 @@ class RMSNorm(Norm):
     (acvram/engine/layers.py:607-630); with ``delta`` the sum x + delta is made first,
     in 32-bit, and written back (acvram/engine/layers.py:633-651)."""
 
-    def __init__(self, hidden_size: int, eps: float, size: int | None = None, tensor: str = "weight") -> None:
-        """``tensor``: the weight's name behind the norm's prefix ("" where the prefix is the whole name)."""
+    def __init__(self, hidden_size: int, eps: float, size: int | None = None, tensor: str = "weight", groups: int = 1) -> None:
+        """``tensor``: the weight's name behind the norm's prefix ("" where the prefix is the whole name).
+        ``groups`` > 1: the row is split into that many equal consecutive parts and each is divided by its own root mean
+        square (the weight still spans the whole row); such a norm wants a float32 residual stream."""
         self.size = size or hidden_size
+        self.groups = int(groups)
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"a norm over {self.size} elements does not split into {groups} equal groups")
         self.eps = float(eps)
         self.tensor = tensor
         self.weight: torch.Tensor | None = None
@@ -31,17 +36,21 @@ class RMSNorm(Norm):
 
     def decode_layer_spec(self):
         """What the fused decode-layer kernel needs of this norm."""
-        return {"weight": self.weight, "eps": self.eps}
+        return {"weight": self.weight, "eps": self.eps} if self.groups == 1 else None
 
     def weight_bytes(self) -> int:
         return 0 if self.weight is None else self.weight.numel() * 4
 
-    def forward(self, x, delta, rows=None, out_dtype=None):
+    def forward(self, x, delta, rows=None, out_dtype=None, delta_scale: float = 1.0):
         """A float32 stream beside parts that run in ``out_dtype`` (bfloat16): sum and norm stay 32-bit, the norm's output
-        is rounded once."""
+        is rounded once.  ``delta_scale``: x += delta_scale * delta (float32 stream only)."""
         n = rows.shape[0] if rows is not None else x.shape[0]
         out_dtype = out_dtype or (delta.dtype if delta is not None else x.dtype)
         out = torch.empty((n, x.shape[1]), device=x.device, dtype=out_dtype)
+        if self.groups > 1 or delta_scale != 1.0 or (x.dtype == torch.float32 and delta is not None and delta.dtype != out_dtype):
+            if x.dtype != torch.float32:
+                raise ValueError("a grouped norm or a factor on the residual wants a float32 residual stream (ModelPlan.residual_dtype)")
+            return ops.add_group_rmsnorm(x, delta, self.weight, self.eps, self.groups, out, rows, delta_scale)
         if x.dtype == torch.float32 and out_dtype != torch.float32:
             return ops.add_rmsnorm_f32(x, delta, self.weight, self.eps, out, rows)
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)

@@ -228,3 +228,97 @@ class GatedLinearRecurrence(SegmentedRecurrence):
         ops.gated_scan(a, b, xy[:, C:], self.y_bias, st.state, ctx.state_slots[st.group], ctx.cu_q, ctx.num_seqs, mixed,
                        work=ctx.work.get(self.metadata_key))
         return self.o(mixed)
+
+
+@register("mixer", "wkv")
+class TimeMix(SegmentedRecurrence):
+    """Time mixing in the manner of RWKV: a linear recurrence per head whose decay depends on the token and on the key
+    channel, with a bonus for the current token.  With h' the previous token's input (zeros before a request's first
+    token) each of r, k, v, g, w reads a mix of its own, x_s = h + (h' - h) * mu_s:
+
+        r, k, v = W_r x_r, W_k x_k, W_v x_v  (heads x dim),     gate = silu(W_g x_g)
+        w = exp(-exp(W_2 tanh(W_1 x_w) + w_0))                    per head and key channel
+        o_t = (S_{t-1} + diag(u) k_t v_t^T)^T r_t;   S_t = diag(w_t) S_{t-1} + k_t v_t^T        S: [dim, dim] per head
+
+    Each head's o is brought to unit RMS (``norm_eps``), the heads side by side are multiplied by a weight and by the gate,
+    and projected by W_o.  The mixer keeps two things for every request: the state S (float32) and the previous token's
+    input.  32-bit in every run precision: the mixes (rounded once as they enter the projections), tanh, the second
+    product, both exponentials, the decays, the recurrence with its state, the head norm and the gate's silu.
+    Tensors behind ``prefix`` (``names`` renames them): mu.r, mu.k, mu.v, mu.g, mu.w, r, k, v, g, w1, w2, w0, u, norm, o."""
+
+    NAMES = {n: n for n in ("mu.r", "mu.k", "mu.v", "mu.g", "mu.w", "r", "k", "v", "g", "w1", "w2", "w0", "u", "norm", "o")}
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, hidden_size: int, num_heads: int, dim: int, norm_eps: float, prefix: str = "mix.",
+                 names: dict | None = None) -> None:
+        self.hidden_size, self.num_heads, self.dim = hidden_size, int(num_heads), int(dim)
+        self.norm_eps = float(norm_eps)
+        self.prefix = prefix
+        self.names = {**self.NAMES, **(names or {})}
+        self.inner_size = self.num_heads * self.dim
+        self.rank = None        # rows of W_1: whatever the file holds
+
+    def _n(self, role: str) -> str:
+        return self.prefix + self.names[role]
+
+    def cache_need(self):
+        return {"state": StateNeed((self.num_heads, self.dim, self.dim), "float32"),
+                "previous": StateNeed((self.hidden_size,), "float32")}
+
+    def tensor_needs(self):
+        H, I = self.hidden_size, self.inner_size
+        needs = {self._n("mu." + s): TensorNeed((H,), "norm") for s in self.MIXES}
+        for role in ("r", "k", "v", "g"):
+            needs[self._n(role)] = TensorNeed((I, H))
+        needs[self._n("w1")] = TensorNeed((-1, H))          # the decay's inner size is the file's to choose
+        needs[self._n("w2")] = TensorNeed((I, -1))
+        needs[self._n("w0")] = TensorNeed((I,), "norm")
+        needs[self._n("u")] = TensorNeed((self.num_heads, self.dim), "norm")
+        needs[self._n("norm")] = TensorNeed((I,), "norm")
+        needs[self._n("o")] = TensorNeed((H, I))
+        return needs
+
+    def load(self, tensors, rt: Runtime) -> None:
+        w = lambda role: tensors[self._n(role)].to(device=rt.device, dtype=rt.dtype)
+        f = lambda role: tensors[self._n(role)].to(device=rt.device, dtype=torch.float32).contiguous()
+        self.mu = torch.stack([f("mu." + s) for s in self.MIXES]).contiguous()      # [5, H], the order of MIXES
+        self.proj = {role: Linear(w(role)) for role in ("r", "k", "v", "g")}
+        self.w1 = Linear(w("w1"))
+        self.rank = self.w1.out_features
+        if tuple(tensors[self._n("w2")].shape) != (self.inner_size, self.rank):
+            raise ValueError(f"wkv: w2 is {tuple(tensors[self._n('w2')].shape)}, w1 has {self.rank} rows")
+        self.w2_t = f("w2").t().contiguous()        # [rank, I]: the threads of a warp read neighbouring channels
+        self.w0, self.u, self.norm_weight = f("w0"), f("u").reshape(-1).contiguous(), f("norm")
+        self.o = Linear(w("o"))
+
+    def weight_bytes(self) -> int:
+        return sum(l.weight_bytes() for l in (*self.proj.values(), self.w1, self.o)) + \
+            sum(t.numel() * 4 for t in (self.mu, self.w2_t, self.w0, self.u, self.norm_weight))
+
+    def flops(self, num_tokens: int) -> float:
+        return sum(l.flops(num_tokens) for l in (*self.proj.values(), self.w1, self.o)) + 2.0 * num_tokens * self.rank * self.inner_size
+
+    def mixing_flops(self, q_lens, kv_lens) -> float:
+        # per token, head and state element: the bonus, the product with r, the decay and the update
+        return 7.0 * self.num_heads * self.dim * self.dim * sum(q_lens)
+
+    def cache_bytes_read(self, q_lens, kv_lens, itemsize: int) -> int:
+        return len(q_lens) * (self.num_heads * self.dim * self.dim + self.hidden_size) * 4
+
+    def forward(self, h, ctx, cache: CacheView):
+        T = h.shape[0]
+        H, D, I = self.num_heads, self.dim, self.inner_size
+        state, previous = cache.parts["state"], cache.parts["previous"]
+        x = torch.empty((len(self.MIXES), T, self.hidden_size), device=h.device, dtype=h.dtype)
+        ops.token_shift_multi(h, self.mu, previous.state, ctx.state_slots[previous.group], ctx.cu_q, ctx.seq_of_token, x)
+        # what enters the recurrence leaves its product unrounded
+        r, k, v = (self.proj[role](x[i], out_dtype=torch.float32) for i, role in enumerate(("r", "k", "v")))
+        gate = self.proj["g"](x[3])
+        decay = torch.empty((T, I), device=h.device, dtype=torch.float32)
+        ops.wkv_decay(self.w1(x[4], out_dtype=torch.float32), self.w2_t, self.w0, decay)
+        o = torch.empty((T, I), device=h.device, dtype=torch.float32)
+        ops.wkv(r, k, v, decay, self.u, state.state, ctx.state_slots[state.group], ctx.cu_q, ctx.num_seqs, o, H, D, D,
+                work=ctx.work.get(self.metadata_key))
+        out = torch.empty((T, I), device=h.device, dtype=h.dtype)
+        ops.retention_gate(o, gate, out, H, D, self.norm_eps, weight=self.norm_weight)
+        return self.o(out)
