@@ -245,3 +245,11 @@ def forward(cfg, W, tokens, streams=None):
             streams.append(X.copy())
     eps, groups = float(cfg["norm"]["eps"]), int(cfg["norm"]["groups"])
     return grouped_norm(X, W["final.norm"], eps, groups) @ W["head"].T
+
+
+def greedy(cfg, W, prompt, new_tokens):
+    """The prompt's continuation by the largest logit, token by token (each time over the whole sequence)."""
+    ids = list(prompt)
+    for _ in range(new_tokens):
+        ids.append(int(np.argmax(forward(cfg, W, ids)[-1])))
+    return ids[len(prompt):]
