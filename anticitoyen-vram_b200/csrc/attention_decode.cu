@@ -26,6 +26,13 @@
 #define AD_WARPS_ALONE 8    // where a CTA has its SM to itself (a grid of no more CTAs than SMs)
 #define AD_LOG2E 1.4426950408889634f
 
+// The merged result of one row: sum / denominator, the denominator holding exp(sink) too where the head has a sink (a
+// score with no key and no value; M and the sums are in the base-2 scale of the scores).
+__device__ __forceinline__ float attn_finish(float O, float L, float M, const float* __restrict__ sinks, int head) {
+    if (sinks && M != -INFINITY) L += exp2f(sinks[head] * AD_LOG2E - M);
+    return L > 0.f ? O / L : 0.f;
+}
+
 template <int D, int NW>
 __global__ void __launch_bounds__(NW * 32)
 attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
@@ -34,7 +41,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
                    const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride,
                    const int* __restrict__ bt_rows, int NH, int NKV, int page_size, int page_shift, int pg_cap, int num_pages, float scale, int window, int chunk_mask, int n_splits,
                    float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters,
-                   int flags) {
+                   int flags, const float* __restrict__ sinks, const float* __restrict__ slopes) {
     const int cluster_merge = flags & 1;        // the splits of a (request, kv-head) are one cluster
     const bool out_f32 = flags & 2;             // out is float (a caller that goes on computing with the result in 32-bit)
     const int keep_first = flags >> 8;          // with a window: the first keys of the request stay visible behind it
@@ -196,6 +203,15 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const float scale_log2 = scale * AD_LOG2E;
     const int mi = lane >> 3, lr = lane & 7;
+    // a distance bias: the score of key j loses slope_h (p - j); this thread's two rows are two query heads of the group
+    float slope_log2[2] = {0.f, 0.f};
+    if (slopes) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = (lane >> 2) + 8 * h;
+            if (r < n_rep) slope_log2[h] = slopes[kvh * n_rep + r] * AD_LOG2E;
+        }
+    }
 
     int stage = 0;
     for (int i = 0; i < my_n; ++i) {
@@ -225,7 +241,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int j = jw + nt * 8 + (lane & 3) * 2 + (e & 1);
-                    const float v = j < end ? s[nt][e] * scale_log2 : -INFINITY;
+                    const float v = j < end ? s[nt][e] * scale_log2 - slope_log2[e >> 1] * (float)(p - j) : -INFINITY;
                     s[nt][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -320,7 +336,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         if (n_splits == 1) {
             {
                 const size_t at = (size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d;
-                const float res = L > 0.f ? O / L : 0.f;
+                const float res = attn_finish(O, L, M, sinks, kvh * n_rep + r);
                 if (out_f32) reinterpret_cast<float*>(out)[at] = res; else out[at] = __float2bfloat16_rn(res);
             }
         } else if (cluster_merge) {
@@ -368,7 +384,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
             }
             {
                 const size_t at = (size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d;
-                const float res = L > 0.f ? O / L : 0.f;
+                const float res = attn_finish(O, L, M, sinks, kvh * n_rep + r);
                 if (out_f32) reinterpret_cast<float*>(out)[at] = res; else out[at] = __float2bfloat16_rn(res);
             }
         }
@@ -423,7 +439,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         }
         {
                 const size_t at = (size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d;
-                const float res = L > 0.f ? O / L : 0.f;
+                const float res = attn_finish(O, L, M, sinks, kvh * n_rep + r);
                 if (out_f32) reinterpret_cast<float*>(out)[at] = res; else out[at] = __float2bfloat16_rn(res);
             }
     }
@@ -525,14 +541,14 @@ static int launch_decode_with(const void* q, int q_stride, void* out, int out_st
                               const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec, const int* kv_len,
                               const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV, int page_size,
                               int page_shift, int pg_cap, int num_pages, float scale, int window, int chunk_mask, int n_splits,
-                              float* part_acc, float* part_ml, int* counters, int cluster_merge, int smem,
-                              cudaStream_t stream) {
+                              float* part_acc, float* part_ml, int* counters, int cluster_merge, const float* sinks,
+                              const float* slopes, int smem, cudaStream_t stream) {
     if (int rc = acv_ensure_smem(decode_smem_config<D, NW>(), attn_decode_kernel<D, NW>, smem)) return rc;
     dim3 grid(n_dec, NKV, n_splits);
     acv_launch_cluster(PDL_ATTN, dim3(1, 1, (cluster_merge & 1) ? n_splits : 1), attn_decode_kernel<D, NW>, grid, NW * 32, smem,
         stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, dec_tokens,
         dec_seqs, kv_len, block_table, bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window,
-        chunk_mask, n_splits, part_acc, part_ml, counters, cluster_merge);
+        chunk_mask, n_splits, part_acc, part_ml, counters, cluster_merge, sinks, slopes);
     return acv_launch_status();
 }
 
@@ -541,7 +557,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                          const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec, const int* kv_len,
                          const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV, int page_size,
                          int num_pages, float scale, int window, int chunk_mask, int n_splits, float* part_acc, float* part_ml, int* counters,
-                         int max_kv, int cluster_merge, cudaStream_t stream) {
+                         int max_kv, int cluster_merge, const float* sinks, const float* slopes, cudaStream_t stream) {
     int page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if ((1 << b) == page_size) page_shift = b;
@@ -554,7 +570,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     const int bound = chunk_mask > 0 && (window <= 0 || chunk_mask < window) ? chunk_mask : window;
 #define AD_LAUNCH_ARGS q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len, block_table, \
                        bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window, chunk_mask, n_splits, \
-                       part_acc, part_ml, counters, cluster_merge | out_f32_bit
+                       part_acc, part_ml, counters, cluster_merge | out_f32_bit, sinks, slopes
     if (decode_grid_has_sms<D>(cluster, (long long)n_dec * NKV * n_splits, &alone)) {
         int smem = decode_smem_bytes(D, NH / NKV, page_size, bound, n_splits, max_kv, cluster_merge, AD_WARPS_ALONE, &pg_cap);
         if (smem < alone) smem = alone;
@@ -572,6 +588,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
 }
 
 // bt_rows (may be null): the row of block_table that belongs to each request of the batch (null: row = its index).
+// sinks, slopes (float [NH], may be null): exp(sink_h) joins the softmax's denominator; key j's score loses slope_h (p - j).
 // Scratch, given by the caller: part_acc holds n_dec*NKV*n_splits*(NH/NKV)*D floats, part_ml
 // n_dec*NKV*n_splits*(NH/NKV)*2 floats, counters n_dec*NKV ints that are zero before the first call
 // (the kernel leaves them zero).  scratch_floats / scratch_counters say how much the caller gave.
@@ -581,7 +598,7 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
                                  int NKV, int D, int page_size, int num_pages, float scale, int window, int chunk_mask, int n_splits, float* part_acc,
                                  float* part_ml, int* counters, long long scratch_floats, long long scratch_ml_floats,
                                  long long scratch_counters, int max_kv, int cluster_merge, int out_f32, int keep_first,
-                                 cudaStream_t stream) {
+                                 const float* sinks, const float* slopes, cudaStream_t stream) {
     if (n_dec <= 0) return 0;
     if (keep_first < 0 || keep_first >= (1 << 22)) return ACV_ERR_SIZE;
     // one word of flags for the kernel: merge inside clusters, float output, and the number of kept first keys
@@ -599,7 +616,7 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
     }
 #define AD_ARGS q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len, block_table, \
                 bt_stride, bt_rows, NH, NKV, page_size, num_pages, scale, window, chunk_mask, n_splits, part_acc, part_ml, counters, max_kv, \
-                cluster_merge, stream
+                cluster_merge, sinks, slopes, stream
     switch (D) {
         case 64: return launch_decode<64>(AD_ARGS);
         case 128: return launch_decode<128>(AD_ARGS);
@@ -698,7 +715,7 @@ ACV_API int acv_attention_decode_static(const void* q, int q_stride, void* out, 
     if (e != cudaSuccess) return (int)e;
     return acv_attention_decode(q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len,
                                 block_table, bt_stride, nullptr, NH, NKV, D, page_size, num_pages, scale, window, 0, n_splits,
-                                part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, 0, 0, 0, stream);
+                                part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, 0, 0, 0, nullptr, nullptr, stream);
 }
 
 ACV_TL_EXPORT(attention_decode)

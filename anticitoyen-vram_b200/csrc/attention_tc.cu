@@ -54,6 +54,8 @@ struct AttnTcParams {
     int out_f32;            // out is float [T, out_stride floats] instead of bfloat16
     float scale;
     int* status;
+    const float* sinks;     // [NH] or null: exp(sink_h) joins the softmax's denominator (a score with no key and no value)
+    const float* slopes;    // [NH] or null: the score of query i and key j loses slope_h (i - j)
 };
 
 template <int D>
@@ -244,6 +246,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const float scale_log2 = p.scale * AT_LOG2E;
         float m_run = -INFINITY, l_run = 0.f;
         bool failed = false;
+        const int head = min(h0 + hs, p.NH - 1);
+        // the distance bias in units of the raw scores: (s - slope (pos - j) / scale) * scale is the biased score
+        const float kappa = p.slopes ? p.slopes[head] / p.scale : 0.f;
 #ifdef ACV_TIMELINE
         unsigned long long tl_acc[5] = {0, 0, 0, 0, 0}, tl_t = acv_tl_now();
 #define TL_PHASE(i) do { const unsigned long long n_ = acv_tl_now(); tl_acc[i] += n_ - tl_t; tl_t = n_; } while (0)
@@ -272,6 +277,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             tc_ld32_nowait(tmem_sx, ra);
             tc_ld32_nowait(tmem_sx + 32, rb);
             tc_wait_ld();
+            if (p.slopes) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    ra[c] = __float_as_uint(fmaf(kappa, (float)(j0 + c - pos), __uint_as_float(ra[c])));
+                    rb[c] = __float_as_uint(fmaf(kappa, (float)(j0 + 32 + c - pos), __uint_as_float(rb[c])));
+                }
+            }
             if (need_mask) { masked(ra, 0); masked(rb, 32); }
 #pragma unroll
             for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], fmaxf(__uint_as_float(ra[c]), __uint_as_float(rb[c])));
@@ -335,6 +347,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #endif
         if (!failed && !abort_s && mbar_wait(o_full + 8 * hs, 0, &abort_s)) {
             tc_fence_after();
+            if (p.sinks && m_run != -INFINITY) l_run += exp2f(p.sinks[head] * AT_LOG2E - m_run);
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             bf16* dst = p.out + (size_t)(tok0 + r) * p.out_stride + (size_t)(h0 + hs) * D;
 #pragma unroll
@@ -392,7 +405,7 @@ ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int 
                              const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_q,
                              const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV,
                              int D, int page_size, int num_pages, float scale, int window, int chunk, int out_f32, int* status,
-                             int keep_first, cudaStream_t stream) {
+                             int keep_first, const float* sinks, const float* slopes, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (NKV <= 0 || NH % NKV || NH > 65535 || (D != 64 && D != 128)) return ACV_ERR_SIZE;
     if ((long long)n_tiles * NH > 0x7fffffffLL) return ACV_ERR_SIZE;
@@ -417,6 +430,9 @@ ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int 
     p.kv_len = kv_len; p.block_table = block_table; p.bt_stride = bt_stride; p.bt_rows = bt_rows; p.NH = NH; p.NKV = NKV;
     p.page_size = page_size; p.page_shift = page_shift; p.num_pages = num_pages; p.window = window; p.chunk = chunk; p.out_f32 = out_f32; p.scale = scale;
     p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
+    p.sinks = sinks;
+    p.slopes = slopes;
+    if (slopes && !(scale > 0.f)) return ACV_ERR_SIZE;
     p.status = status;
     if (D == 64) return launch_attn_tc<64>(mq, mk, mv, p, n_tiles, stream);
     return launch_attn_tc<128>(mq, mk, mv, p, n_tiles, stream);

@@ -108,8 +108,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, P, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
         "acv_gemm_tc_bias": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P, P],
-        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, P, I, I, I, I, I, F, I, I, I, P, P, P, LL, LL, LL, I, I, I, I, P],
-        "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, P, I, P],
+        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, P, I, I, I, I, I, F, I, I, I, P, P, P, LL, LL, LL, I, I, I, I, P, P, P],
+        "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, P, I, P, P, P],
         "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, I, I, P],
         "acv_table_update": [P, I, I, P, I, P],
         "acv_embed_scaled": [P, P, P, I, I, I, F, I, P],
@@ -748,12 +748,15 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
                      dec_tokens: torch.Tensor, dec_seqs: torch.Tensor, n_dec: int, kv_len: torch.Tensor,
                      block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                      window: int, n_splits: int, max_kv: int = 0, cluster_merge: bool = True,
-                     table_rows: torch.Tensor | None = None, chunk: int = 0, keep_first: int = 0) -> torch.Tensor:
+                     table_rows: torch.Tensor | None = None, chunk: int = 0, keep_first: int = 0,
+                     sinks: torch.Tensor | None = None, slopes: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of requests that bring one token each, over their pages, split over the context.
+    ``sinks``, ``slopes`` (float32 [heads]): as in ``attention_generic``; the sink joins once, where the splits merge.
 
     Up to 8 splits are merged inside a thread-block cluster (through its shared memory); more, or
     ``cluster_merge=False``, go through partial results in scratch memory and a last-arriver merge."""
     n_rep = num_heads // num_kv_heads
+    _head_vectors(num_heads, sinks, slopes)
     use_cluster = cluster_merge and 1 < n_splits <= 8
     parts = n_dec * num_kv_heads * n_splits if n_splits > 1 and not use_cluster else 0
     acc, ml, cnt = _decode_scratch(q.device, parts * n_rep * head_dim, parts * n_rep * 2, n_dec * num_kv_heads)
@@ -762,7 +765,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
         _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads, head_dim,
         k_pages.shape[2], k_pages.shape[0], scale, window, chunk, n_splits, _p(acc), _p(ml), _p(cnt), acc.numel(), ml.numel(), cnt.numel(),
         max_kv or block_table.shape[1] * k_pages.shape[2], 1 if use_cluster else 0,
-        1 if out.dtype == torch.float32 else 0, int(keep_first), _stream()), "attention_decode")
+        1 if out.dtype == torch.float32 else 0, int(keep_first), _p(sinks), _p(slopes), _stream()), "attention_decode")
     return out
 
 
@@ -783,14 +786,17 @@ def attention_chunk(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v
 def attention_tc(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                  tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor, kv_len: torch.Tensor,
                  block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                 window: int, table_rows: torch.Tensor | None = None, chunk: int = 0, keep_first: int = 0) -> torch.Tensor:
-    """Causal attention of portions of prompts on tcgen05 (tiles of QUERY_TILE query tokens, pages by TMA)."""
+                 window: int, table_rows: torch.Tensor | None = None, chunk: int = 0, keep_first: int = 0,
+                 sinks: torch.Tensor | None = None, slopes: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of portions of prompts on tcgen05 (tiles of QUERY_TILE query tokens, pages by TMA).
+    ``sinks``, ``slopes`` (float32 [heads]): as in ``attention_generic``."""
+    _head_vectors(num_heads, sinks, slopes)
     _, _, status = _gemm_buffers(q.device, 0, 0)
     _check(library().acv_attention_tc(
         _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0),
         n_tiles, _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads,
         head_dim, k_pages.shape[2], k_pages.shape[0], scale, window, chunk, 1 if out.dtype == torch.float32 else 0, _p(status),
-        int(keep_first), _stream()), "attention_tc")
+        int(keep_first), _p(sinks), _p(slopes), _stream()), "attention_tc")
     return out
 
 
@@ -873,7 +879,9 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
     # kept first keys: the split-KV decode kernel and the tcgen05 portion kernel know them, the mma.sync portion kernel does not
     if not generic and keep_first > 0 and (chunk > 0 or (w["n_tiles"] and not attention_tc_takes(qkv, out, k_pages, head_dim))):
         generic = True
-    if sinks is not None or slopes is not None:
+    # sinks and slopes: the generic, the split-KV and the tcgen05 portion kernel know them, the mma.sync portion kernel does not
+    if not generic and (sinks is not None or slopes is not None) and (chunk > 0 or (
+            w["n_tiles"] and not attention_tc_takes(qkv, out, k_pages, head_dim))):
         generic = True
     if generic:
         if chunk > 0:
@@ -888,11 +896,12 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
             decode_plan(w["n_dec"], num_heads, num_kv_heads, head_dim, k_pages.shape[2], kv)
         attention_decode(qkv, out, k_pages, v_pages, w["dec_tokens"], w["dec_seqs"], w["n_dec"], ctx.kv_len,
                          block_table, num_heads, num_kv_heads, head_dim, scale, window, n_splits, w["max_dec_kv"],
-                         cluster_merge=in_clusters, table_rows=rows, chunk=chunk, keep_first=keep_first)
+                         cluster_merge=in_clusters, table_rows=rows, chunk=chunk, keep_first=keep_first, sinks=sinks,
+                         slopes=slopes)
     if w["n_tiles"] and attention_tc_takes(qkv, out, k_pages, head_dim):
         attention_tc(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
                      block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows, chunk=chunk,
-                     keep_first=keep_first)
+                     keep_first=keep_first, sinks=sinks, slopes=slopes)
     elif w["n_tiles"]:
         attention_chunk(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
                         block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows,

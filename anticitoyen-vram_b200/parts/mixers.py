@@ -196,7 +196,8 @@ class Attention(Mixer):
         applied by table, and no biases)."""
         rotary = self.position.rotary_table()
         if self.qkv.bias is not None or self.o.bias is not None or rotary is None or rotary.shape[1] != self.head_dim \
-                or self.value_dim != self.head_dim or self.keep_first or self.out_scale != 1.0:
+                or self.value_dim != self.head_dim or self.keep_first or self.out_scale != 1.0 or self.wide \
+                or self.sinks is not None or self.slopes is not None or self.score is not None:
             return None
         return {"num_heads": self.num_heads, "num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim,
                 "window": self.window, "scale": self.scale, "w_qkv": self.qkv.weight, "w_o": self.o.weight,
