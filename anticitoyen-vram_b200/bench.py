@@ -234,8 +234,8 @@ def time_parts(runner, q_lens: list, kv_lens: list, reps: int = 5, layer: int = 
     entry = model.plan.schedule[layer]
     block = model.blocks[entry.layer]
     view = model._cache_view(runner.storage, entry)
-    if getattr(block, "token_shift", None) is not None:      # the block keeps a row of its own beside its mixer's cache
-        view = view.parts.get("mixer")
+    if getattr(block, "token_shift", None) is not None or getattr(block, "input_conv", None) is not None:
+        view = view.parts.get("mixer")      # (the block keeps rows of its own beside its mixer's cache)
     T = sum(q_lens)
     h = (torch.randn((T, model.plan.hidden_size), device=dev) * 0.5).to(runner.rt.dtype)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -256,6 +256,9 @@ def time_parts(runner, q_lens: list, kv_lens: list, reps: int = 5, layer: int = 
     out = {}
     try:
         mixer, ff = block.mixer, block.feed_forward
+        share = getattr(mixer, "value_share", None)
+        if share is not None and share["role"] == "mix":    # what an earlier layer of the step would have left
+            ctx.shared[share["key"]] = torch.zeros((T, mixer.v_size), device=dev, dtype=torch.float32)
         ms = timed(lambda: mixer.forward(h, ctx, view))
         itemsize = runner.rt.dtype.itemsize
         out["mixer"] = {"ms": ms, "flops": mixer.flops(T) + mixer.mixing_flops(q_lens, kv_lens),

@@ -837,6 +837,7 @@ ACV_API int acv_decode_layer(const DlLayerArgs* a, cudaStream_t stream) {
         if (Ks[i] % 8 || ((uintptr_t)Ws[i] & 15) || ((uintptr_t)Bs[i] & 15) || ((uintptr_t)Cs[i] & 15) || (ldcs[i] % 8)) return ACV_ERR_ALIGN;
         gp.RA = Ns[i]; gp.RB = T; gp.K = Ks[i]; gp.M = T; gp.N = Ns[i]; gp.ldc = ldcs[i]; gp.swap = 1; gp.out_f32 = 0;
         gp.act = i == 2 ? 1 : 0; gp.qkv = i == 0 ? 1 : 0; gp.staged = 1; gp.cluster = 0; gp.early_w = 1;
+        gp.gate_fn = 0; gp.unary = 0; gp.row_scale = nullptr;
         gp.C = Cs[i]; gp.workspace = a->workspace; gp.counters = a->counters; gp.status = a->status;
         gp.wait_limit = GT_WAIT_LIMIT; gp.skip_kb = -1;
         gp.q_heads = NH; gp.kv_heads = NKV; gp.head_dim = D; gp.q_w = a->q_norm; gp.k_w = a->k_norm; gp.qk_eps = a->qk_eps;

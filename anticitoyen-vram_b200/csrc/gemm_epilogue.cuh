@@ -19,8 +19,12 @@ struct GemmParams {
                             // 2: the same pairs through a clamped gated unit, scaled by the row first (tokens on rows only):
                             //    g = min(w gate, limit), u = clamp(w up, +-limit), C = g * sigmoid(alpha g) * (u + 1)
     const float* bias;      // float [N]: added to the product's feature n before anything else is made of it (null: none)
-    const float* row_scale; // act 2: w of each row of A (null: 1)
+    const float* row_scale; // act 2, and act 0 with tokens on rows: w of each row of A (null: 1)
     float glu_limit, glu_alpha;
+    int gate_fn;            // act 1: what the gate passes through: 0 silu (with the roundings of the unfused path), 1 the tanh
+                            // form of gelu (in float on the accumulators, the product rounded once)
+    int unary;              // act 0 with tokens on rows: an activation on every output, after the row's scale
+                            // (1 gelu by tanh, 2 silu, 3 gelu by erf; 0: none)
     // grouped product (tokens on rows): tile ta of A multiplies the rows [tile_expert[ta] * N, +N) of the B operand,
     // which stacks `experts` matrices of N rows; only the first *tiles_used tiles of A exist
     const int* tile_expert;
@@ -68,6 +72,21 @@ __device__ __forceinline__ bf16 swiglu_pair(float gate, float up) {
     return __float2bfloat16_rn(s * u);
 }
 
+// gelu_tanh(gate) * up in float on the accumulators, rounded once.
+__device__ __forceinline__ bf16 geglu_pair(float gate, float up) {
+    const float t = tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate));
+    return __float2bfloat16_rn(0.5f * gate * (1.f + t) * up);
+}
+__device__ __forceinline__ bf16 gated_pair(float gate, float up, int fn) { return fn ? geglu_pair(gate, up) : swiglu_pair(gate, up); }
+
+// An activation on one output (GemmParams.unary), in float.
+__device__ __forceinline__ float unary_act(float z, int kind) {
+    if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (kind == 2) return __fdividef(z, 1.f + __expf(-z));
+    if (kind == 3) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
+    return z;
+}
+
 // The clamped gated unit of act 2, in float, rounded once.
 __device__ __forceinline__ bf16 glu_clamped_pair(float gate, float up, float w, float limit, float alpha) {
     const float g = fminf(gate * w, limit);
@@ -79,13 +98,13 @@ __device__ __forceinline__ bf16 glu_clamped_pair(float gate, float up, float w, 
 // share the work: each sends the other the eight values that it does not need, the even lane makes the tokens 0..7,
 // the odd lane the tokens 8..15 (all exchanges first, then the arithmetic, so that the eight chains run side by
 // side: done token by token, with the odd lane idle, this took 75 ns a token).  Returns the first of this lane's tokens.
-__device__ __forceinline__ int swiglu_lane_pair(const float (&v)[16], int lane, bf16 (&o)[8]) {
+__device__ __forceinline__ int swiglu_lane_pair(const float (&v)[16], int lane, bf16 (&o)[8], int fn = 0) {
     const bool odd = lane & 1;
     float other[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) other[c] = __shfl_xor_sync(0xffffffffu, odd ? v[c] : v[c + 8], 1);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) o[c] = swiglu_pair(odd ? other[c] : v[c], odd ? v[c + 8] : other[c]);
+    for (int c = 0; c < 8; ++c) o[c] = gated_pair(odd ? other[c] : v[c], odd ? v[c + 8] : other[c], fn);
     return odd ? 8 : 0;
 }
 
@@ -105,13 +124,15 @@ __device__ __forceinline__ void gt_add_bias(const GemmParams& p, int row_a, int 
     }
 }
 
+__device__ __forceinline__ void gt_store16_rows(const GemmParams& p, int row_a, int col0, const float (&v)[16]);
+
 // Write 16 accumulator columns of one tensor-memory lane: row_a is the A-operand row the lane holds,
 // col0 the B-operand row of v[0].  Executed by whole warps (the paired form shuffles between lanes).
 __device__ __forceinline__ void gt_store16(const GemmParams& p, int row_a, int col0, const float (&v)[16], int lane) {
     if (p.act) {
         if (p.swap) {       // features lie on lanes: an even lane holds a gate, the next lane its up
             bf16 o[8];
-            const int first = swiglu_lane_pair(v, lane, o);
+            const int first = swiglu_lane_pair(v, lane, o, p.gate_fn);
             const int f = row_a & ~1;           // the pair's gate row
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -127,7 +148,7 @@ __device__ __forceinline__ void gt_store16(const GemmParams& p, int row_a, int c
                 for (int k = 0; k < 8; ++k) o[k] = glu_clamped_pair(v[2 * k], v[2 * k + 1], w, p.glu_limit, p.glu_alpha);
             } else {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) o[k] = swiglu_pair(v[2 * k], v[2 * k + 1]);
+                for (int k = 0; k < 8; ++k) o[k] = gated_pair(v[2 * k], v[2 * k + 1], p.gate_fn);
             }
             if (col0 + 16 <= p.N && (((uintptr_t)dst) & 15) == 0) {
                 *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
@@ -152,6 +173,21 @@ __device__ __forceinline__ void gt_store16(const GemmParams& p, int row_a, int c
             }
         }
     } else if (row_a < p.M) {
+        if (p.row_scale || p.unary) {       // a row's own factor, then an activation, on copies of the accumulators
+            float u[16];
+            const float w = p.row_scale ? p.row_scale[row_a] : 1.f;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) u[c] = unary_act(v[c] * w, p.unary);
+            gt_store16_rows(p, row_a, col0, u);
+            return;
+        }
+        gt_store16_rows(p, row_a, col0, v);
+    }
+}
+
+// (the tail of gt_store16 for tokens on rows: 16 neighbouring features of one token)
+__device__ __forceinline__ void gt_store16_rows(const GemmParams& p, int row_a, int col0, const float (&v)[16]) {
+    {
         if (p.out_f32) {
             float* dst = (float*)p.C + (size_t)row_a * p.ldc + col0;
 #pragma unroll
@@ -182,7 +218,7 @@ __device__ __forceinline__ void gt_store16(const GemmParams& p, int row_a, int c
 __device__ __forceinline__ void gt_stage16(const GemmParams& p, unsigned char* stage, int f, int col0, const float (&v)[16], int lane) {
     if (p.act) {            // an even lane holds a gate, the next lane its up: 64 output features per tile
         bf16 o[8];
-        const int first = swiglu_lane_pair(v, lane, o);
+        const int first = swiglu_lane_pair(v, lane, o, p.gate_fn);
 #pragma unroll
         for (int c = 0; c < 8; ++c) reinterpret_cast<bf16*>(stage)[(col0 + first + c) * 64 + (f >> 1)] = o[c];
     } else if (p.out_f32) {

@@ -815,7 +815,14 @@ static int gemm_tc_run(GemmParams& p, const void* x, int ldx, const void* w, int
     const void* b_ptr = swap ? x : w;
     p.RA = swap ? N : M;
     p.RB = swap ? M : N;
-    p.K = K; p.M = M; p.N = N; p.ldc = ldc; p.swap = swap; p.out_f32 = out_f32; p.act = act; p.cluster = flags & 1; p.early_w = (flags >> 1) & 1;
+    p.K = K; p.M = M; p.N = N; p.ldc = ldc; p.swap = swap; p.out_f32 = out_f32; p.cluster = flags & 1; p.early_w = (flags >> 1) & 1;
+    // act's low four bits say what becomes of the outputs (0, 1, 2 as GemmParams.act has them), the bits above them which
+    // function: the gate's of act 1, or the activation that act 0 puts on every output
+    p.act = act & 15;
+    p.gate_fn = p.act == 1 ? act >> 4 : 0;
+    p.unary = p.act == 0 ? act >> 4 : 0;
+    act = p.act;
+    if (p.gate_fn > 1 || p.unary > 3 || ((p.unary || (p.row_scale && act == 0)) && (swap || splits > 1))) return ACV_ERR_SIZE;
     if (act && (out_f32 || (N & 1))) return ACV_ERR_SIZE;
     if (act == 2 && swap) return ACV_ERR_SIZE;
     if (p.tile_expert && (swap || splits > 1 || (flags & 6) || p.experts < 1 || (N % 8))) return ACV_ERR_SIZE;

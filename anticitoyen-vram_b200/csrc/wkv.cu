@@ -67,28 +67,46 @@ ACV_API int acv_token_shift_multi(const void* h, const float* mu, float* state, 
 
 // ----------------------------------------------------------------------------- the decay
 // a: float [T, L] (the first product's output); w2t: float [L, C] (the second matrix transposed); w0: float [C];
-// w: float [T, C].  One block a token; tanh of the L inputs once, in shared memory.
+// w: float [T, C].  One block for WD_TOK tokens: tanh of their L inputs once, in shared memory; a thread owns channels
+// and walks the L rows of the matrix once for all of the block's tokens.
+#define WD_TOK 8
 __global__ void wkv_decay_kernel(const float* __restrict__ a, int lda, const float* __restrict__ w2t,
-                                 const float* __restrict__ w0, float* __restrict__ w, int C, int L) {
-    extern __shared__ float th[];
+                                 const float* __restrict__ w0, float* __restrict__ w, int T_tokens, int C, int L) {
+    extern __shared__ float th[];           // [L][WD_TOK]
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
-    for (int j = threadIdx.x; j < L; j += blockDim.x) th[j] = tanhf(a[(size_t)t * lda + j]);
+    const int t0 = blockIdx.x * WD_TOK;
+    const int n = min(WD_TOK, T_tokens - t0);
+    for (int i = threadIdx.x; i < L * WD_TOK; i += blockDim.x) {
+        const int j = i / WD_TOK, tt = i - j * WD_TOK;
+        th[i] = tt < n ? tanhf(a[(size_t)(t0 + tt) * lda + j]) : 0.f;
+    }
     __syncthreads();
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float z = w0[c];
-        for (int j = 0; j < L; ++j) z = fmaf(w2t[(size_t)j * C + c], th[j], z);
-        w[(size_t)t * C + c] = expf(-expf(z));
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float z[WD_TOK];
+        const float z0 = w0[c];
+#pragma unroll
+        for (int tt = 0; tt < WD_TOK; ++tt) z[tt] = z0;
+        for (int j = 0; j < L; ++j) {
+            const float m = w2t[(size_t)j * C + c];
+#pragma unroll
+            for (int tt = 0; tt < WD_TOK; ++tt) z[tt] = fmaf(m, th[j * WD_TOK + tt], z[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < WD_TOK; ++tt)
+            if (tt < n) w[(size_t)(t0 + tt) * C + c] = expf(-expf(z[tt]));
     }
 }
 
 ACV_API int acv_wkv_decay(const float* a, int lda, const float* w2t, const float* w0, float* w, int T_tokens, int C, int L,
                           cudaStream_t stream) {
     if (T_tokens <= 0) return 0;
-    if (C <= 0 || L <= 0 || L > 8192) return ACV_ERR_SIZE;
-    acv_launch(PDL_MISC, wkv_decay_kernel, T_tokens, C >= 1024 ? 256 : 128, (size_t)L * sizeof(float), stream, a, lda, w2t, w0,
-               w, C, L);
+    if (C <= 0 || L <= 0 || L > 1024) return ACV_ERR_SIZE;
+    const int blocks_t = (T_tokens + WD_TOK - 1) / WD_TOK;
+    // few tokens: the channels are spread over several blocks as well, so that a decoding batch fills more than a few SMs
+    const int blocks_c = blocks_t >= 148 ? 1 : min((C + 127) / 128, 16);
+    acv_launch(PDL_MISC, wkv_decay_kernel, dim3(blocks_t, blocks_c), 128, (size_t)L * WD_TOK * sizeof(float), stream, a, lda,
+               w2t, w0, w, T_tokens, C, L);
     return acv_launch_status();
 }
 

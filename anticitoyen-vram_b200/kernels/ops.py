@@ -73,7 +73,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, P, I, I, I, I, F, P],
         "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P],
         "acv_add_group_rmsnorm": [P, P, F, P, P, P, I, I, I, F, I, I, P],
-        "acv_input_conv": [P, P, P, P, P, P, P, I, I, I, I, P],
+        "acv_input_conv": [P, P, P, P, P, P, P, I, I, I, I, P, P],
         "acv_add_group_rmsnorm_conv": [P, P, F, P, P, P, P, P, I, I, I, F, I, I, I, P],
         "acv_qkv_prepare": [P, I, I, I, I, I, I, P, P, F, P, I, I, F, I, I, F, P, I, F, P, P, P, I, P, P, P, I, I, I, P],
         "acv_token_shift_multi": [P, P, P, P, P, P, P, I, I, I, I, P],
@@ -461,7 +461,8 @@ def gemm_tc_plan(M: int, N: int, K: int, sms: int | None = None, bn_multiple: in
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | None = None,
-            swiglu_pairs: bool = False, static_weights: bool = False, bias: torch.Tensor | None = None) -> torch.Tensor:
+            swiglu_pairs: bool = False, static_weights: bool = False, bias: torch.Tensor | None = None,
+            gate_fn: int = 0) -> torch.Tensor:
     """out[M,N] = x[M,K] @ w[N,K]^T (+ bias) on tcgen05; x, w bfloat16, out bfloat16 or float32; ``bias`` float32 [N],
     added in the epilogue to the float accumulator (before the activation of the paired form).
 
@@ -469,7 +470,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | N
     read its first tiles while the kernel before it in the stream is still running.
 
     With ``swiglu_pairs`` the rows of w come in (gate, up) pairs and out is [M, N/2]:
-    out[:, i] = silu(x . w[2i]) * (x . w[2i+1]), rounded as the separate kernels round."""
+    out[:, i] = silu(x . w[2i]) * (x . w[2i+1]), rounded as the separate kernels round; with ``gate_fn`` 1 the gate
+    passes through the tanh form of gelu instead (in float on the accumulators, the product rounded once)."""
     _need_cuda(x, w, out)
     M, K = x.shape
     N = w.shape[0]
@@ -487,7 +489,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | N
     tiles = (-(-N // 128) * -(-M // bn)) if swap else (-(-M // 128) * -(-N // bn))
     ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)
     args = (_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K,
-            1 if out.dtype == torch.float32 else 0, 1 if swiglu_pairs else 0, swap, bn, splits, _p(ws), ws.numel(), _p(cnt),
+            1 if out.dtype == torch.float32 else 0, (1 | (int(gate_fn) << 4)) if swiglu_pairs else 0, swap, bn, splits, _p(ws),
+            ws.numel(), _p(cnt),
             cnt.numel(), _p(status), sm_count(x.device), stages, cluster | (2 if static_weights else 0))
     if bias is not None:
         if bias.dtype != torch.float32 or bias.numel() != N or not bias.is_contiguous():
@@ -989,10 +992,11 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, static_weig
 
 
 def linear_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor,
-                       static_weights: bool = False, bias: torch.Tensor | None = None) -> torch.Tensor:
+                       static_weights: bool = False, bias: torch.Tensor | None = None, act: int = 1) -> torch.Tensor:
     """out[M, I] = silu(x @ Wg^T + bg) * (x @ Wu^T + bu) in one kernel; w_pairs [2I, K] holds (gate_i, up_i) in rows
-    2i, 2i+1, and ``bias`` (float32 [2I]) their biases in the same order."""
-    return gemm_tc(x, w_pairs, out, swiglu_pairs=True, static_weights=static_weights, bias=bias)
+    2i, 2i+1, and ``bias`` (float32 [2I]) their biases in the same order.  ``act``: a code of ``GATED_EPILOGUE_ACTS``
+    (1: silu; 2: the tanh form of gelu on the gate)."""
+    return gemm_tc(x, w_pairs, out, swiglu_pairs=True, static_weights=static_weights, bias=bias, gate_fn=act - 1)
 
 
 def linear_bf16_f32out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, static_weights: bool = False,
@@ -1173,10 +1177,13 @@ def moe_gather(h: torch.Tensor, grouped: torch.Tensor, weights: torch.Tensor | N
 
 
 def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_expert: torch.Tensor, tiles_used: torch.Tensor,
-                    glu: bool = False, row_scale: torch.Tensor | None = None, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
+                    glu: bool = False, row_scale: torch.Tensor | None = None, limit: float = 0.0, alpha: float = 0.0,
+                    unary: str | None = None) -> torch.Tensor:
     """The experts' products on tcgen05: x [tiles * 128, K] holds the rows in grouped order, w [E, N, K] the experts'
     matrices; out [rows, N] (bfloat16 or float32), or with ``glu`` [rows, N / 2] bfloat16: w's rows come in (gate, up) pairs
-    and go through the clamped gated unit, the accumulators times ``row_scale[row]`` first."""
+    and go through the clamped gated unit, the accumulators times ``row_scale[row]`` first.  Without ``glu``:
+    ``row_scale`` multiplies a row's accumulators, and ``unary`` (a name of ``ACTIVATIONS`` other than the first) is then
+    applied to every output, in float."""
     _need_cuda(x, w, out, tile_expert, tiles_used)
     E, N, K = w.shape
     M = x.shape[0]
@@ -1188,7 +1195,8 @@ def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_ex
     bn = 256 if N >= 256 else (128 if N >= 128 else 64)
     _, _, status = _gemm_buffers(x.device, 0, 0)
     _check(library().acv_gemm_tc_grouped(_p(x), x.stride(0), _p(w), K, _p(out), out.stride(0), M, N, K, E, _p(tile_expert),
-                                         _p(tiles_used), 1 if out.dtype == torch.float32 else 0, 2 if glu else 0,
+                                         _p(tiles_used), 1 if out.dtype == torch.float32 else 0,
+                                         2 if glu else ((ACTIVATIONS[unary] << 4) if unary else 0),
                                          _p(row_scale), limit, alpha, bn, _p(status), sm_count(x.device), 8, _stream()),
            "gemm_tc_grouped")
     return out
@@ -1628,7 +1636,7 @@ def cast_rows_f32(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 ACTIVATIONS = {"xielu": 0, "gelu_tanh": 1, "silu": 2, "gelu": 3}
 # gate activations that the tensor-core product applies in its own epilogue: name -> the epilogue's code
-GATED_EPILOGUE_ACTS = {"silu": 1}
+GATED_EPILOGUE_ACTS = {"silu": 1, "gelu_tanh": 2}
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, kind: str, p0: float = 0.0, p1: float = 0.0) -> torch.Tensor:
@@ -1755,17 +1763,20 @@ def add_group_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch
 
 
 def input_conv(h: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor,
-               seq_of_token: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+               seq_of_token: torch.Tensor, out: torch.Tensor, taps_t: torch.Tensor | None = None) -> torch.Tensor:
     """out[t] = h[t] + sum_j taps[:, j] * h[t - K + 1 + j] along each request's tokens (h float32 [T, C], taps float32
-    [C, K]); the rows before the step come from ``state`` (float32 [slots, K-1, C], oldest first), which is replaced."""
+    [C, K]); the rows before the step come from ``state`` (float32 [slots, K-1, C], oldest first), which is replaced.
+    ``taps_t``: the taps transposed ([K, C], float32): a thread then takes four neighbouring channels."""
     _need_cuda(h, taps, state, out)
     T, C = h.shape
     K = taps.shape[1]
     if h.dtype != torch.float32 or taps.dtype != torch.float32 or state.dtype != torch.float32 or not h.is_contiguous() \
             or not taps.is_contiguous() or not state.is_contiguous() or not out.is_contiguous() or taps.shape[0] != C:
         raise KernelError("input_conv: contiguous float32 input, taps [C, K] and state are wanted")
+    if taps_t is not None and (taps_t.dtype != torch.float32 or not taps_t.is_contiguous() or taps_t.shape != (K, C)):
+        taps_t = None
     _check(library().acv_input_conv(_p(h), _p(taps), _p(state), _p(slots), _p(cu_q), _p(seq_of_token), _p(out), T, C, K,
-                                    dtype_code(out.dtype), _stream()), "input_conv")
+                                    dtype_code(out.dtype), _p(taps_t), _stream()), "input_conv")
     return out
 
 

@@ -84,6 +84,7 @@ class PreNormBlock:
             self.shift_mu = tensors[self.token_shift].to(device=rt.device, dtype=torch.float32).contiguous()
         if self.input_conv is not None:
             self.conv_taps = tensors[self.input_conv["tensor"]].to(device=rt.device, dtype=torch.float32).contiguous()
+            self.conv_taps_t = self.conv_taps.t().contiguous()
 
     def cache_need(self):
         need = self.mixer.cache_need()
@@ -122,7 +123,7 @@ class PreNormBlock:
             return ops.add_group_rmsnorm_conv(x, delta, n.weight, n.eps, n.groups, self.conv_taps, conv_view.state, slots, out,
                                               scale.get("delta_scale", 1.0))
         normed = n.forward(x, delta, out_dtype=torch.float32, **scale)
-        return ops.input_conv(normed, self.conv_taps, conv_view.state, slots, ctx.cu_q, ctx.seq_of_token, out)
+        return ops.input_conv(normed, self.conv_taps, conv_view.state, slots, ctx.cu_q, ctx.seq_of_token, out, self.conv_taps_t)
 
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in (self.input_norm, self.post_norm, self.mixer, self.feed_forward) if p is not None)

@@ -187,6 +187,8 @@ class RoutedExperts(FeedForward):
             torch.stack([w(f"e{e}.gate"), w(f"e{e}.up")], dim=1).reshape(2 * self.expert_ff, self.hidden_size) if self.pairs
             else torch.cat([w(f"e{e}.gate"), w(f"e{e}.up")], dim=0) for e in range(self.experts)]).contiguous()
         self.down = torch.stack([w(f"e{e}.down") for e in range(self.experts)]).contiguous()
+        # plain experts on the grouped tcgen05 product: bfloat16 with rows of 16-byte alignment
+        self.tc_plain = self.plain and rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.expert_ff % 8 == 0
         self.shared_gate_up = self.shared_down = self.shared_gate = None
         if self.shared_ff and self.plain:
             self.shared_pairs = False
@@ -260,7 +262,23 @@ class RoutedExperts(FeedForward):
         place = torch.empty(rows, device=dev, dtype=torch.int32)
         w_in = weights if self.weight_on == "input" else None
         w_out = weights if self.weight_on == "output" else None
-        if self.pairs and rows >= ops.MOE_TC_ROWS and rows >= ops.MOE_TC_ROWS_PER_EXPERT * E and w_out is None:
+        if self.tc_plain and rows >= ops.MOE_TC_ROWS and rows >= ops.MOE_TC_ROWS_PER_EXPERT * E:
+            # plain experts, many rows: the same grouping; the activation is the first product's epilogue, the row's weight
+            # the second's (on the float accumulators)
+            tile = ops.MOE_TC_TILE
+            tiles = ops.moe_max_tiles(rows, E, tile)
+            grouped = torch.empty(tiles * tile, device=dev, dtype=torch.int32)
+            tile_expert = torch.empty(tiles, device=dev, dtype=torch.int32)
+            used = torch.empty(1, device=dev, dtype=torch.int32)
+            ops.moe_group(ids, E, grouped, place, tile_expert, tile, used)
+            hg = torch.empty((tiles * tile, H), device=dev, dtype=h.dtype)
+            scale = torch.empty(tiles * tile, device=dev, dtype=torch.float32)
+            ops.moe_gather(h, grouped, weights, top, hg, scale, used, tile)
+            act = torch.empty((tiles * tile, F), device=dev, dtype=h.dtype)
+            ops.gemm_tc_grouped(hg, self.gate_up, act, tile_expert, used, unary=self.activation)
+            parts = torch.empty((tiles * tile, H), device=dev, dtype=h.dtype)
+            ops.gemm_tc_grouped(act, self.down, parts, tile_expert, used, row_scale=scale)
+        elif self.pairs and rows >= ops.MOE_TC_ROWS and rows >= ops.MOE_TC_ROWS_PER_EXPERT * E and w_out is None:
             # many rows: tiles of 128 rows on the tcgen05 product, the tokens' rows copied into grouped order first
             tile = ops.MOE_TC_TILE
             tiles = ops.moe_max_tiles(rows, E, tile)

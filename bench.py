@@ -323,6 +323,105 @@ NIZEDRA_SIZES = {
 }
 
 
+VADELIX_SIZES = {
+    # width, norm groups, taps; attention (both kinds): heads, kv heads, head size (keys and values), rotated part, window of
+    # the windowed kind; time mixing: heads, head size; gated feed-forward size; mixture: experts, choices, groups, kept
+    # groups, an expert's size, the shared expert's
+    "s": dict(width=2048, groups=4, taps=4, heads=16, kv_heads=4, dim=128, rot=64, window=1024, t_heads=32, t_dim=64, ff=6144,
+              experts=32, top=4, e_groups=8, e_keep=4, e_ff=768, shared_ff=1536),
+    "m": dict(width=4096, groups=4, taps=4, heads=32, kv_heads=8, dim=128, rot=64, window=2048, t_heads=64, t_dim=64, ff=12288,
+              experts=64, top=6, e_groups=8, e_keep=4, e_ff=1024, shared_ff=2048),
+}
+
+
+def run_vadelix(args) -> int:
+    """``--design vadelix``: prefill and decode throughput of the Vadelix design at layer sizes of real models (random
+    weights; six layers: time mixing, rotated attention with sinks, windowed attention with slopes, twice, gated
+    feed-forwards and mixtures in turn), beside a Qwen3 model of equal size: the same width, as many attention heads of
+    the same size, the gated feed-forward's size.  Whole steps through the step function, and the mixer and feed-forward
+    of each kind of layer alone with their rooflines (L2 flushed before each timed run).  One JSON line."""
+    import torch
+
+    from acvram_b200 import bench as B
+    from acvram_b200.config import Qwen3Config, VadelixConfig
+    from acvram_b200.engine.runner import ModelRunner
+    from acvram_b200.models import build_random
+
+    pk, pk_src = peaks()
+    K, W = args.steps, args.warmup
+    page = 64
+    layers, vocab = args.layers or 6, 32768
+    out = {"design": "vadelix", "beside": "qwen3", "layers": layers, "vocab": vocab, "dtype": "bf16", "page_size": page,
+           "data": "synthetic token ids, random weights", "peaks": {**pk, "source": pk_src}, "sizes": {}}
+    for name in args.sizes.split(","):
+        z = VADELIX_SIZES[name]
+        dense = {"kind": "dense", "ff": z["ff"]}
+        moe = {"kind": "moe", "expert": {"ff": z["e_ff"]}, "shared": {"ff": z["shared_ff"]},
+               "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["e_groups"], "keep": z["e_keep"]}}}
+        heads = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                 "v_mix": True}
+        mixers = (("wkv", {"heads": z["t_heads"], "dim": z["t_dim"]}),
+                  ("attention", {**heads, "rot": {"base": 1e6, "dims": z["rot"],
+                                                  "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}),
+                  ("attention_2", {**heads, "mask": {"size": z["window"]}, "q_temp": {"coef": 0.1, "every": 512}}))
+        vcfg = VadelixConfig.from_dict({
+            "architecture": "Vadelix", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6, "groups": z["groups"]},
+            "residual_mult": 0.7, "canon": {"taps": z["taps"]},
+            "layers": [{"type": mixers[i % 3][0], "mixer": mixers[i % 3][1], "mlp": moe if i % 2 else dense} for i in range(layers)]})
+        qcfg = Qwen3Config(vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=layers,
+                           num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                           rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=8192, tie_word_embeddings=False)
+        res = {"vadelix": dict(z), "qwen3": {"hidden": qcfg.hidden_size, "intermediate": qcfg.intermediate_size,
+                                            "q_heads": qcfg.num_attention_heads, "kv_heads": qcfg.num_key_value_heads,
+                                            "head_dim": qcfg.head_dim}}
+        for arm, cfg in (("vadelix", vcfg), ("qwen3", qcfg)):
+            model = build_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0")
+            batch_max = 64
+            tokens = batch_max * (args.context + 2 * (K + W) + 2 * page) + 4096
+            runner = ModelRunner(model, page, tokens // page + 8, batch_max + 2, max_len=8192)
+            if not args.no_cuda_graphs:
+                runner.enable_graphs()
+            r = {"weights_gb": round(model.weight_bytes() / 1e9, 3)}
+            try:
+                pre = B.time_prefill(runner, 2048, reps=5, warmup=3)
+                flops = B.prefill_flops(model, 2048)
+                r["prefill_2048"] = {"tokens_per_s": round(pre["tokens_per_s"], 1), "ms": round(pre["ms"], 3),
+                                     "tflops_frac": round(flops / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+                for b in (8, 64):
+                    names = [f"d{b}-{i}" for i in range(b)]
+                    B.fill_contexts(runner, names, args.context)
+                    try:
+                        d = B.time_decode(runner, names, K, W)
+                    finally:
+                        for n in names:
+                            runner.release(n)
+                    nbytes = B.decode_step_bytes(model, b, args.context + W + K // 2)
+                    r[f"decode_b{b}"] = {"tokens_per_s": round(d["tokens_per_s"], 1), "ms_per_step": round(d["ms_per_step"], 4),
+                                         "hbm_frac": round(nbytes / (d["ms_per_step"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+                # layer 0: time mixing + gated unit; 1: rotated attention + mixture; 2: windowed attention
+                kinds = (("wkv", 0), ("attention", 1), ("window", 2)) if arm == "vadelix" and layers > 2 else (("", 0),)
+                for kind, layer in kinds:
+                    for label, ql, kl in (("prefill_2048", [2048], [2048]), ("decode_b64", [1] * 64, [args.context] * 64)):
+                        parts = B.time_parts(runner, ql, kl, layer=layer)
+                        for part, v in parts.items():
+                            if part == "feed_forward" and layer > 1:
+                                continue        # the feed-forwards of layers 0 and 1 are the two kinds
+                            sec = v["ms"] * 1e-3
+                            label_part = ("gated_unit" if layer == 0 else "mixture") if part == "feed_forward" and kind else part
+                            r[f"{kind + '_' if kind and part == 'mixer' else ''}{label_part}_{label}"] = {
+                                "us": round(v["ms"] * 1e3, 1),
+                                "tflops_frac": round(v["flops"] / sec / (pk["bf16_tflops"] * 1e12), 4),
+                                "hbm_frac": round(v["bytes"] / sec / 1e9 / pk["hbm_gbs"], 4)}
+            except B.Refused as exc:
+                r["refused"] = str(exc)
+            res[arm + "_result"] = r
+            del runner, model
+            _free_device_memory()
+        out["sizes"][name] = res
+    print(json.dumps(out))
+    return 0
+
+
 def run_nizedra(args) -> int:
     """``--design nizedra``: prefill and decode throughput of the Nizedra design at layer sizes of real models (random
     weights; six layers: mixed-heads attention, lightning, latent attention, twice), beside a Qwen3 model of equal size:
@@ -595,7 +694,7 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16, help="tokens in a page of the cache (the engine's own default is 64)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-cuda-graphs", action="store_true")
-    ap.add_argument("--design", default="", choices=["", "zotonex", "redudra", "nizedra"],
+    ap.add_argument("--design", default="", choices=["", "zotonex", "redudra", "nizedra", "vadelix"],
                     help="measure another design beside its closest relative instead of the headline (see run_design)")
     ap.add_argument("--sizes", default="s,m", help="with --design: which of its sizes (s: width 2048, m: width 4096)")
     ap.add_argument("--time-limit", type=float, default=240.0,
@@ -612,6 +711,8 @@ def main() -> int:
         return run_redudra(args)
     if args.design == "nizedra":
         return run_nizedra(args)
+    if args.design == "vadelix":
+        return run_vadelix(args)
     if args.design:
         return run_design(args)
     return run_ours(args)

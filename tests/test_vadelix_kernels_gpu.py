@@ -104,7 +104,7 @@ def test_grouped_norm_and_convolution_over_steps(H, groups, taps, dtype):
         else:
             normed = torch.empty(x.shape, device=DEV)
             ops.add_group_rmsnorm(x, d, dev(w), eps, groups, normed, None, mult)
-            ops.input_conv(normed, dev(tp), state, slots, cu, seq_of, out)
+            ops.input_conv(normed, dev(tp), state, slots, cu, seq_of, out, dev(tp.T.copy()) if H % 8 == 0 else None)
         o = 0
         for r, a, c in step:
             got_h[r][a:a + c] = out[o:o + c].float().cpu().numpy()
@@ -370,7 +370,8 @@ def test_routing_by_groups(E, top, count, keep):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("T,H,F,E,top", [(1, 64, 48, 4, 1), (9, 96, 40, 6, 2), (70, 100, 36, 5, 2), (300, 128, 64, 8, 3)])
+@pytest.mark.parametrize("T,H,F,E,top", [(1, 64, 48, 4, 1), (9, 96, 40, 6, 2), (70, 100, 36, 5, 2), (300, 128, 64, 8, 3),
+                                         (700, 128, 64, 8, 3), (1500, 256, 192, 4, 1)])      # (the last two: grouped tcgen05 products)
 def test_plain_experts(T, H, F, E, top, dtype):
     """The part as a whole against the oracle's mixture (softmax scores, groups, weights on the outputs, a shared expert
     without a gate), on weights and inputs that bfloat16 holds."""
