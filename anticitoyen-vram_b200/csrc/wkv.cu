@@ -103,8 +103,8 @@ ACV_API int acv_wkv_decay(const float* a, int lda, const float* w2t, const float
     if (T_tokens <= 0) return 0;
     if (C <= 0 || L <= 0 || L > 1024) return ACV_ERR_SIZE;
     const int blocks_t = (T_tokens + WD_TOK - 1) / WD_TOK;
-    // few tokens: the channels are spread over several blocks as well, so that a decoding batch fills more than a few SMs
-    const int blocks_c = blocks_t >= 148 ? 1 : min((C + 127) / 128, 16);
+    // a thread owns one channel (a block 128 of them): enough blocks for every SM whatever the number of tokens
+    const int blocks_c = min((C + 127) / 128, 65535);
     acv_launch(PDL_MISC, wkv_decay_kernel, dim3(blocks_t, blocks_c), 128, (size_t)L * WD_TOK * sizeof(float), stream, a, lda,
                w2t, w0, w, T_tokens, C, L);
     return acv_launch_status();
@@ -127,7 +127,8 @@ wkv_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict
            const float* __restrict__ u, float* __restrict__ state, const int* __restrict__ slots,
            const int* __restrict__ cu_q, WkvSegments sg, float* __restrict__ o, int ldo, int H, int D, int DV, int G, int TC,
            int DVT) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
+    const bool whole_rows = D % R == 0;     // (R is a multiple of four, so D is one as well, and rows of k, r, w are 16-byte pieces)
     float* rs = sm;                         // [TC][D]
     float* ks = rs + (size_t)TC * D;        // [TC][D]
     float* ws = ks + (size_t)TC * D;        // [TC][D]
@@ -192,13 +193,31 @@ wkv_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict
                 const float* rr = rs + tt * D + g * R;
                 const float* wr = ws + tt * D + g * R;
                 float part = 0.f;
+                if (whole_rows) {       // every group's rows lie inside the head: 16-byte loads of k, r and w
 #pragma unroll
-                for (int i = 0; i < R; ++i) {
-                    if (g * R + i < D) {
-                        const float kv = kr[i] * vv;
-                        if (!SUMMARY) part = fmaf(fmaf(U[i], kv, S[i]), rr[i], part);
-                        S[i] = fmaf(wr[i], S[i], kv);
-                        if (SUMMARY) P[i] *= wr[i];
+                    for (int i4 = 0; i4 < R / 4; ++i4) {
+                        const float4 k4 = reinterpret_cast<const float4*>(kr)[i4], w4 = reinterpret_cast<const float4*>(wr)[i4];
+                        float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (!SUMMARY) r4 = reinterpret_cast<const float4*>(rr)[i4];
+                        const float kx[4] = {k4.x, k4.y, k4.z, k4.w}, wx[4] = {w4.x, w4.y, w4.z, w4.w}, rx[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int i = i4 * 4 + e;
+                            const float kv = kx[e] * vv;
+                            if (!SUMMARY) part = fmaf(fmaf(U[i], kv, S[i]), rx[e], part);
+                            S[i] = fmaf(wx[e], S[i], kv);
+                            if (SUMMARY) P[i] *= wx[e];
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < R; ++i) {
+                        if (g * R + i < D) {
+                            const float kv = kr[i] * vv;
+                            if (!SUMMARY) part = fmaf(fmaf(U[i], kv, S[i]), rr[i], part);
+                            S[i] = fmaf(wr[i], S[i], kv);
+                            if (SUMMARY) P[i] *= wr[i];
+                        }
                     }
                 }
                 if (!SUMMARY) red[((size_t)tt * G + g) * DVT + cl] = part;
