@@ -294,6 +294,35 @@ def retention_case(q_len: int, batch: int, reps: int, H: int = 16, D: int = 64, 
             "gbs": nbytes / us / 1e3}
 
 
+def wkv_case(q_len: int, batch: int, reps: int, H: int = 32, D: int = 64, C: int = 2048, rank: int = 32) -> dict:
+    """Time mixing's own kernels for ``batch`` requests that bring ``q_len`` tokens each: the five mixes of the token
+    shift, the decays, and the recurrence of 32 heads of 64 x 64 with decays of the token's own."""
+    dev = "cuda"
+    T = q_len * batch
+    cu, seq_of, _, slots, work = _steps(q_len, batch)
+    h = torch.randn(T, C, device=dev).to(torch.bfloat16)
+    mu = torch.rand(5, C, device=dev)
+    prev = torch.zeros(batch, C, device=dev)
+    x = torch.empty(5, T, C, device=dev, dtype=torch.bfloat16)
+    r, k, v = (torch.randn(T, H * D, device=dev) for _ in range(3))
+    a = torch.randn(T, rank, device=dev)
+    w2_t, w0 = torch.randn(rank, H * D, device=dev) / rank ** 0.5, torch.full((H * D,), -2.0, device=dev)
+    decay = torch.empty(T, H * D, device=dev)
+    u = torch.randn(H * D, device=dev)
+    state = torch.zeros(batch, H, D, D, device=dev)
+    o = torch.empty(T, H * D, device=dev)
+    us_shift = _time(lambda i: ops.token_shift_multi(h, mu, prev, slots, cu, seq_of, x), reps)
+    us_decay = _time(lambda i: ops.wkv_decay(a, w2_t, w0, decay), reps)
+    us = _time(lambda i: ops.wkv(r, k, v, decay, u, state, slots, cu, batch, o, H, D, D, work=work), reps)
+    flops = 7.0 * T * H * D * D * (1.5 if work["summaries"] else 1.0)
+    nbytes = 2 * state.numel() * 4 + T * H * D * 4 * 5
+    print(f"wkv q_len={q_len} batch={batch} heads={H} of {D}x{D}: {us:.1f} us ({flops / us / 1e6:.2f} TFLOP/s float, "
+          f"{nbytes / us / 1e3:.0f} GB/s), token shift {us_shift:.1f} us ({T * C * 12 / us_shift / 1e3:.0f} GB/s), "
+          f"decays {us_decay:.1f} us")
+    return {"kernel": "wkv", "q_len": q_len, "batch": batch, "us": us, "us_shift": us_shift, "us_decay": us_decay,
+            "tflops": flops / us / 1e6, "gbs": nbytes / us / 1e3}
+
+
 def recurrence_case(q_len: int, batch: int, reps: int, C: int = 4096, blocks: int = 16, taps: int = 4) -> dict:
     """The gated linear recurrence's kernels for ``batch`` requests of ``q_len`` tokens: 4096 channels in 16 blocks."""
     dev = "cuda"
@@ -431,6 +460,9 @@ CASES = {
     "latent_attention_decode_b64": lambda r: latent_attention_case(1, 64, 2048, r),
     "retention_prefill": lambda r: retention_case(2048, 1, r),
     "retention_decode_b64": lambda r: retention_case(1, 64, r),
+    "wkv_prefill": lambda r: wkv_case(2048, 1, r),
+    "wkv_prefill_small": lambda r: wkv_case(512, 1, r),
+    "wkv_decode_b64": lambda r: wkv_case(1, 64, r),
     "recurrence_prefill": lambda r: recurrence_case(2048, 1, r),
     "recurrence_decode_b64": lambda r: recurrence_case(1, 64, r),
     "norm_shift_prefill": lambda r: norm_shift_case(2048, 1, r),
