@@ -19,7 +19,6 @@
 // S_in(z+1) = diag(P(z)) S_in(z) + S_seg(z); a last launch walks every segment again from what lies in front of it and
 // writes the outputs.  Steps of short portions and single tokens run the last launch alone.
 #include "common.cuh"
-#include <stdlib.h>
 
 // ----------------------------------------------------------------------------- token shift with several mixes
 // h: [T, C] of type T; mu: float [S, C]; out: [S, T, C] of type T; state: float [slots, C].  grid (tokens, channel tiles).
@@ -338,8 +337,7 @@ ACV_API int acv_wkv(const void* r, const void* k, const void* v, int ld, const f
     // block has 512 threads at most (three arrays of R registers a thread)
     const int DVT = DV <= 128 ? DV : 128;
     int R = 4;
-    static const int want = getenv("WKV_THREADS") ? atoi(getenv("WKV_THREADS")) : 512;
-    while (R < 32 && ((D + R - 1) / R) * DVT > want) R *= 2;
+    while (R < 32 && ((D + R - 1) / R) * DVT > 512) R *= 2;     // (measured at 64 x 64: blocks of 512 threads 238 us for 2048 tokens, of 256 and 128 threads 288 and 290)
     if (((D + R - 1) / R) * DVT > wkv_max_threads(R)) return ACV_ERR_SIZE;
     if (dtype == ACV_F32)
         return wkv_by_rows<float>(R, r, k, v, ld, w, u, state, slots, cu_q, sg, summaries, o, ldo, n_items, H, D, DV, DVT, stream);
