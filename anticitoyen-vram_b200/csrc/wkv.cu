@@ -18,7 +18,8 @@
 // first one from the request's state) and the product of its decays per key channel; a small launch folds them,
 // S_in(z+1) = diag(P(z)) S_in(z) + S_seg(z); a last launch walks every segment again from what lies in front of it and
 // writes the outputs.  Steps of short portions and single tokens run the last launch alone.
-#include "common.cuh"
+#include "mma_tiles.cuh"
+#include <type_traits>
 
 // ----------------------------------------------------------------------------- token shift with several mixes
 // h: [T, C] of type T; mu: float [S, C]; out: [S, T, C] of type T; state: float [slots, C].  grid (tokens, channel tiles).
@@ -126,14 +127,13 @@ __global__ void __launch_bounds__(wkv_max_threads(R))
 wkv_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, int ld, const float* __restrict__ w,
            const float* __restrict__ u, float* __restrict__ state, const int* __restrict__ slots,
            const int* __restrict__ cu_q, WkvSegments sg, float* __restrict__ o, int ldo, int H, int D, int DV, int G, int TC,
-           int DVT) {
+           int DVT, int prefetch) {
     extern __shared__ __align__(16) float sm[];
     const bool whole_rows = D % R == 0;     // (R is a multiple of four, so D is one as well, and rows of k, r, w are 16-byte pieces)
-    float* rs = sm;                         // [TC][D]
-    float* ks = rs + (size_t)TC * D;        // [TC][D]
-    float* ws = ks + (size_t)TC * D;        // [TC][D]
-    float* vs = ws + (size_t)TC * D;        // [TC][DVT]
-    float* red = vs + (size_t)TC * DVT;     // [TC][G][DVT]
+    // two sets of staged tokens (with `prefetch`: float inputs in 16-byte pieces, the next chunk copied asynchronously
+    // while this one is computed; otherwise the first set alone is used), then the chunk's partial sums
+    const size_t set = (size_t)TC * (3 * D + DVT);
+    float* red = sm + 2 * set;              // [TC][G][DVT]
     pdl_launch_dependents();
     pdl_wait();
     const int item = blockIdx.x, h = blockIdx.y;
@@ -172,8 +172,42 @@ wkv_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict
         U[i] = (g < G && d < D) ? u[(size_t)h * D + d] : 0.f;
         P[i] = 1.f;
     }
-    for (int tb = t0; tb < t1; tb += TC) {
+    // a chunk's tokens as 16-byte pieces, asynchronously: rows of r, k, w (D floats) and of v (DVT floats)
+    auto prefetch_chunk = [&](int tb, int n, float* base) {
+        if constexpr (std::is_same<T, float>::value) {
+            const int d4 = D >> 2, v4 = DVT >> 2;
+            float* rs_ = base; float* ks_ = rs_ + (size_t)TC * D; float* ws_ = ks_ + (size_t)TC * D; float* vs_ = ws_ + (size_t)TC * D;
+            for (int i = tid; i < n * d4; i += nthr) {
+                const int tt = i / d4, e = (i - tt * d4) << 2;
+                const size_t at = (size_t)(tb + tt) * ld + (size_t)h * D + e;
+                if (!SUMMARY) cp_async16(smem_u32(rs_ + tt * D + e), r + at, true);
+                cp_async16(smem_u32(ks_ + tt * D + e), k + at, true);
+                cp_async16(smem_u32(ws_ + tt * D + e), w + (size_t)(tb + tt) * H * D + (size_t)h * D + e, true);
+            }
+            for (int i = tid; i < n * v4; i += nthr) {
+                const int tt = i / v4, e = (i - tt * v4) << 2;
+                const bool in = c0 + e < DV;
+                cp_async16(smem_u32(vs_ + tt * DVT + e), in ? (const void*)(v + (size_t)(tb + tt) * ld + (size_t)h * DV + c0 + e) : (const void*)v, in);
+            }
+        }
+    };
+    if (prefetch) {
+        prefetch_chunk(t0, min(TC, t1 - t0), sm);
+        cp_async_commit();
+    }
+    int turn = 0;
+    for (int tb = t0; tb < t1; tb += TC, turn ^= 1) {
         const int n = min(TC, t1 - tb);
+        float* rs = sm + (prefetch ? turn * set : 0);   // [TC][D]
+        float* ks = rs + (size_t)TC * D;                 // [TC][D]
+        float* ws = ks + (size_t)TC * D;                 // [TC][D]
+        float* vs = ws + (size_t)TC * D;                 // [TC][DVT]
+        if (prefetch) {
+            // the other set was read in the turn before this one, whose last barrier every thread has passed
+            if (tb + TC < t1) prefetch_chunk(tb + TC, min(TC, t1 - tb - TC), sm + (turn ^ 1) * set);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
         for (int i = tid; i < n * D; i += nthr) {
             const int tt = i / D, e = i - tt * D;
             const size_t at = (size_t)(tb + tt) * ld + (size_t)h * D + e;
@@ -184,6 +218,7 @@ wkv_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict
         for (int i = tid; i < n * DVT; i += nthr) {
             const int tt = i / DVT, e = i - tt * DVT;
             vs[i] = c0 + e < DV ? to_f32(v[(size_t)(tb + tt) * ld + (size_t)h * DV + c0 + e]) : 0.f;
+        }
         }
         __syncthreads();
         if (owner) {
@@ -283,8 +318,11 @@ static int launch_wkv(const void* r, const void* k, const void* v, int ld, const
                       int D, int DV, int DVT, cudaStream_t stream) {
     const int G = (D + R - 1) / R;
     const int threads = ((G * DVT + 31) / 32) * 32;
-    const size_t per_token = (size_t)(3 * D + DVT + G * DVT) * sizeof(float);
+    const size_t per_token = (size_t)(2 * (3 * D + DVT) + G * DVT) * sizeof(float);
     const dim3 grid(n_items, H, (DV + DVT - 1) / DVT);
+    // float inputs whose rows are 16-byte pieces are copied asynchronously, a chunk ahead
+    const int prefetch = std::is_same<T, float>::value && D % 4 == 0 && DV % 4 == 0 && DVT % 4 == 0 && ld % 4 == 0 &&
+                         !((uintptr_t)r & 15) && !((uintptr_t)k & 15) && !((uintptr_t)v & 15) && !((uintptr_t)w & 15);
     int TC = (int)((48 * 1024) / per_token);
     TC = TC > 32 ? 32 : TC;
     if (TC < 1) TC = 1;
@@ -298,11 +336,11 @@ static int launch_wkv(const void* r, const void* k, const void* v, int ld, const
     }
     if (summaries) {
         acv_launch(PDL_ATTN, wkv_kernel<T, R, true>, grid, threads, smem, stream, (const T*)r, (const T*)k, (const T*)v, ld, w, u,
-                   state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC, DVT);
+                   state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC, DVT, prefetch);
         acv_launch(PDL_ATTN, wkv_fold_kernel, dim3(n_items, H, (D * DV + 255) / 256), 256, 0, stream, sg, cu_q, H, D, DV);
     }
     acv_launch(PDL_ATTN, wkv_kernel<T, R, false>, grid, threads, smem, stream, (const T*)r, (const T*)k, (const T*)v, ld, w, u,
-               state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC, DVT);
+               state, slots, cu_q, sg, o, ldo, H, D, DV, G, TC, DVT, prefetch);
     return acv_launch_status();
 }
 
