@@ -14,7 +14,7 @@
 // thread only, whatever else runs in the step.
 #include "common.cuh"
 
-#define GN_MAX_GROUPS 32
+#define GN_MAX_GROUPS 4096      // the groups' sums wait in shared memory behind the row
 
 // four neighbouring elements at once (16 bytes of float, 8 of bfloat16)
 __device__ __forceinline__ float4 gn_ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -55,7 +55,7 @@ __global__ void add_group_rmsnorm_kernel(float* __restrict__ x, const TD* __rest
                                          const float* __restrict__ w, TO* __restrict__ out, const int* __restrict__ rows,
                                          int H, int G, float eps) {
     extern __shared__ __align__(16) float row[];
-    __shared__ float red[GN_MAX_GROUPS];
+    float* red = row + H;                   // [G]
     pdl_launch_dependents();
     pdl_wait();
     const int r_out = blockIdx.x;
@@ -104,7 +104,7 @@ __global__ void add_group_rmsnorm_kernel(float* __restrict__ x, const TD* __rest
 template <typename TD, typename TO>
 static int launch_group_norm(float* x, const void* delta, float delta_scale, const float* w, void* out, const int* rows,
                              int n_rows, int H, int G, float eps, cudaStream_t stream) {
-    const size_t smem = (size_t)H * sizeof(float);
+    const size_t smem = (size_t)(H + G) * sizeof(float);
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
     const bool vec = H % 4 == 0 && (H / G) % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)delta & 15) && !((uintptr_t)w & 15) &&
                      !((uintptr_t)out & 15);
@@ -127,7 +127,7 @@ ACV_API int acv_add_group_rmsnorm(float* x, const void* delta, float delta_scale
                                   int n_rows, int H, int groups, float eps, int delta_dtype, int out_dtype,
                                   cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (groups < 1 || groups > GN_MAX_GROUPS || H % groups || (size_t)H * 4 > 200 * 1024) return ACV_ERR_SIZE;
+    if (groups < 1 || groups > GN_MAX_GROUPS || H % groups || (size_t)(H + groups) * 4 > 200 * 1024) return ACV_ERR_SIZE;
     if (!delta) delta_dtype = out_dtype;
 #define GN_CASE(D, TD, O, TO)                                                                                        \
     if (delta_dtype == D && out_dtype == O)                                                                           \
@@ -269,7 +269,7 @@ __global__ void add_group_rmsnorm_conv_kernel(float* __restrict__ x, const TD* _
                                               float* __restrict__ state, const int* __restrict__ slots, TO* __restrict__ out,
                                               int H, int G, float eps, int K) {
     extern __shared__ float row[];
-    __shared__ float red[GN_MAX_GROUPS];
+    float* red = row + H;                   // [G]
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
@@ -307,7 +307,7 @@ template <typename TD, typename TO>
 static int launch_group_norm_conv(float* x, const void* delta, float delta_scale, const float* w, const float* taps,
                                   float* state, const int* slots, void* out, int n_rows, int H, int G, float eps, int K,
                                   cudaStream_t stream) {
-    const size_t smem = (size_t)H * sizeof(float);
+    const size_t smem = (size_t)(H + G) * sizeof(float);
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
     if (smem > 48 * 1024) {
         static AcvSmemConfig cfg;
@@ -322,7 +322,7 @@ ACV_API int acv_add_group_rmsnorm_conv(float* x, const void* delta, float delta_
                                        float* state, const int* slots, void* out, int n_rows, int H, int groups, float eps,
                                        int K, int delta_dtype, int out_dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (groups < 1 || groups > GN_MAX_GROUPS || H % groups || (size_t)H * 4 > 200 * 1024 || K < 1) return ACV_ERR_SIZE;
+    if (groups < 1 || groups > GN_MAX_GROUPS || H % groups || (size_t)(H + groups) * 4 > 200 * 1024 || K < 1) return ACV_ERR_SIZE;
     if (!delta) delta_dtype = out_dtype;
 #define GN_CASE(D, TD, O, TO)                                                                                        \
     if (delta_dtype == D && out_dtype == O)                                                                           \

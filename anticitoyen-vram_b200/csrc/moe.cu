@@ -59,7 +59,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int h_stride, const fl
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * MR_WARPS + warp;
     if (t >= T_tokens) return;
-    float* sc = sm_all + warp * E;
+    float* sc = sm_all + warp * (E + n_groups);
     if (z) {
         for (int e = lane; e < E; e += 32) sc[e] = z[(size_t)t * ldz + e];
         if (gate && lane == 0) gate[t] = 1.f / (1.f + expf(-z[(size_t)t * ldz + E]));
@@ -99,25 +99,35 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int h_stride, const fl
     __syncwarp();
     if (n_groups > 1 && keep_groups < n_groups) {
         // The experts stand in n_groups equal groups of neighbours; a group is worth its best score, and only the
-        // keep_groups best groups (ties: the lower index) can be chosen from.  Lane g holds group g's worth.
+        // keep_groups best groups (ties: the lower index) can be chosen from.  gw: the groups' worths, behind the scores;
+        // a kept group's worth is replaced by a mark.
         const int per = E / n_groups;
-        float worth = -INFINITY;
-        if (lane < n_groups)
-            for (int e = lane * per; e < (lane + 1) * per; ++e) worth = fmaxf(worth, sc[e]);
-        unsigned kept = 0;
+        float* gw = sc + E;
+        for (int g = lane; g < n_groups; g += 32) {
+            float worth = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) worth = fmaxf(worth, sc[e]);
+            gw[g] = worth;
+        }
+        __syncwarp();
+        const float KEPT = INFINITY;
         for (int j = 0; j < keep_groups; ++j) {
-            float best = (kept >> lane) & 1u ? -INFINITY : worth;
-            int arg = lane < n_groups && !((kept >> lane) & 1u) ? lane : 0x7fffffff;
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) {
+                const float x = gw[g];
+                if (x != KEPT && (arg == 0x7fffffff || x > best)) { best = x; arg = g; }    // ascending g: the first of equals stays
+            }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
                 const float ob = __shfl_xor_sync(0xffffffffu, best, o);
                 const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
                 if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
             }
-            if (arg != 0x7fffffff) kept |= 1u << arg;
+            if (lane == 0 && arg != 0x7fffffff) gw[arg] = KEPT;
+            __syncwarp();
         }
         for (int e = lane; e < E; e += 32)
-            if (!((kept >> (e / per)) & 1u)) sc[e] = -INFINITY;
+            if (gw[e / per] != KEPT) sc[e] = -INFINITY;
         __syncwarp();
     }
     float total = 0.f;
@@ -153,8 +163,8 @@ ACV_API int acv_moe_route(const void* h, int h_stride, const float* w_router, co
     if (T_tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || E > 4096) return ACV_ERR_SIZE;
     if (n_groups < 1) n_groups = 1;
-    if (n_groups > 32 || E % n_groups || keep_groups < 1 || (n_groups > 1 && top > keep_groups * (E / n_groups))) return ACV_ERR_SIZE;
-    const size_t smem = (size_t)MR_WARPS * E * sizeof(float);
+    if (E % n_groups || keep_groups < 1 || (n_groups > 1 && top > keep_groups * (E / n_groups))) return ACV_ERR_SIZE;
+    const size_t smem = (size_t)MR_WARPS * (E + n_groups) * sizeof(float);
     const int grid = (T_tokens + MR_WARPS - 1) / MR_WARPS;
     if (dtype == ACV_F32)
         acv_launch(PDL_MISC, moe_route_kernel<float>, grid, MR_WARPS * 32, smem, stream, (const float*)h, h_stride, w_router,

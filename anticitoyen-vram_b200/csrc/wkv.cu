@@ -373,7 +373,8 @@ ACV_API int acv_wkv(const void* r, const void* k, const void* v, int ld, const f
     sg.seq = seg_seq; sg.idx = seg_idx; sg.len = seg_len; sg.state = seg_state; sg.decay = seg_decay;
     // value columns of a block: all of them up to 128; rows of the state a thread keeps: the fewest with which the
     // block has 512 threads at most (three arrays of R registers a thread)
-    const int DVT = DV <= 128 ? DV : 128;
+    int DVT = DV <= 128 ? DV : 128;
+    while (DVT > 32 && ((D + 31) / 32) * DVT > 512) DVT = (DVT / 2 + 3) & ~3;      // (a very long key: fewer columns a block)
     int R = 4;
     while (R < 32 && ((D + R - 1) / R) * DVT > 512) R *= 2;     // (measured at 64 x 64: blocks of 512 threads 238 us for 2048 tokens, of 256 and 128 threads 288 and 290)
     if (((D + R - 1) / R) * DVT > wkv_max_threads(R)) return ACV_ERR_SIZE;

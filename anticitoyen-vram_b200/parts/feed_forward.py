@@ -147,7 +147,7 @@ class RoutedExperts(FeedForward):
         self.groups = (int(groups[0]), int(groups[1])) if groups else None
         if self.groups is not None:
             count, keep = self.groups
-            if count < 1 or experts % count or not 1 <= keep <= count or top > keep * (experts // count) or count > 32:
+            if count < 1 or experts % count or not 1 <= keep <= count or top > keep * (experts // count):
                 raise ValueError(f"{experts} experts in {count} groups of which {keep} are kept cannot give {top} choices")
         self.renorm_eps = float(renorm_eps)
         self.shared_gated = bool(shared_gate)

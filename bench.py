@@ -327,9 +327,9 @@ VADELIX_SIZES = {
     # width, norm groups, taps; attention (both kinds): heads, kv heads, head size (keys and values), rotated part, window of
     # the windowed kind; time mixing: heads, head size; gated feed-forward size; mixture: experts, choices, groups, kept
     # groups, an expert's size, the shared expert's
-    "s": dict(width=2048, groups=4, taps=4, heads=16, kv_heads=4, dim=128, rot=64, window=1024, t_heads=32, t_dim=64, ff=6144,
+    "s": dict(width=2048, groups=8, taps=4, heads=16, kv_heads=4, dim=128, rot=64, window=1024, t_heads=32, t_dim=64, ff=6144,
               experts=32, top=4, e_groups=8, e_keep=4, e_ff=768, shared_ff=1536),
-    "m": dict(width=4096, groups=4, taps=4, heads=32, kv_heads=8, dim=128, rot=64, window=2048, t_heads=64, t_dim=64, ff=12288,
+    "m": dict(width=4096, groups=8, taps=4, heads=32, kv_heads=8, dim=128, rot=64, window=2048, t_heads=64, t_dim=64, ff=12288,
               experts=64, top=6, e_groups=8, e_keep=4, e_ff=1024, shared_ff=2048),
 }
 
@@ -366,7 +366,7 @@ def run_vadelix(args) -> int:
                   ("attention_2", {**heads, "mask": {"size": z["window"]}, "q_temp": {"coef": 0.1, "every": 512}}))
         vcfg = VadelixConfig.from_dict({
             "architecture": "Vadelix", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6, "groups": z["groups"]},
-            "residual_mult": 0.7, "canon": {"taps": z["taps"]},
+            "residual_mult": 0.5, "canon": {"taps": z["taps"]},
             "layers": [{"type": mixers[i % 3][0], "mixer": mixers[i % 3][1], "mlp": moe if i % 2 else dense} for i in range(layers)]})
         qcfg = Qwen3Config(vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=layers,
                            num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],

@@ -78,7 +78,7 @@ def segments(q_lens, seg_len):
 
 # --------------------------------------------------------------------------- grouped norm and the input convolution
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,groups,taps", [(32, 1, 1), (96, 3, 3), (100, 5, 5), (1024, 4, 4), (2048, 16, 2)])
+@pytest.mark.parametrize("H,groups,taps", [(32, 1, 1), (96, 3, 3), (100, 5, 5), (1024, 4, 4), (2048, 16, 2), (256, 64, 6)])
 def test_grouped_norm_and_convolution_over_steps(H, groups, taps, dtype):
     """Three requests side by side, cut differently, their kept rows in slots 5, 0 and 2; steps in which every request
     brings one token take the fused launch.  The stream after the sums and the mixer's input must be the oracle's."""
@@ -278,7 +278,8 @@ def test_the_source_layer_leaves_its_values():
 
 # --------------------------------------------------------------------------- time mixing
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,D,rank,seg", [(3, 16, 8, 0), (1, 32, 4, 4), (5, 12, 6, 3), (2, 64, 16, 4), (2, 128, 32, 0), (4, 48, 8, 5)])
+@pytest.mark.parametrize("H,D,rank,seg", [(3, 16, 8, 0), (1, 32, 4, 4), (5, 12, 6, 3), (2, 64, 16, 4), (2, 128, 32, 0), (4, 48, 8, 5),
+                                          (2, 10, 3, 2), (1, 256, 8, 4)])
 def test_time_mixing_over_steps(H, D, rank, seg, dtype):
     """Token shift with five mixes, the decays and the recurrence for three requests side by side, cut differently
     (portions longer than a segment run the three launches), their states in slots 4, 1 and 3 (zero at first, as the
@@ -352,7 +353,8 @@ def test_a_long_portion_in_segments_equals_token_by_token():
 
 
 # --------------------------------------------------------------------------- experts without gates, chosen by groups
-@pytest.mark.parametrize("E,top,count,keep", [(6, 2, 3, 2), (4, 1, 1, 1), (5, 2, 5, 2), (8, 3, 4, 2), (64, 6, 8, 3), (32, 4, 32, 4)])
+@pytest.mark.parametrize("E,top,count,keep", [(6, 2, 3, 2), (4, 1, 1, 1), (5, 2, 5, 2), (8, 3, 4, 2), (64, 6, 8, 3), (32, 4, 32, 4),
+                                              (128, 5, 64, 7), (96, 3, 48, 47)])
 def test_routing_by_groups(E, top, count, keep):
     from acvram_b200.kernels import ops
     rng = np.random.default_rng(E + top)
