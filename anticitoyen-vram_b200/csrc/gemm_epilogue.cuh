@@ -23,7 +23,7 @@ struct GemmParams {
     float glu_limit, glu_alpha;
     int gate_fn;            // act 1: what the gate passes through: 0 silu (with the roundings of the unfused path), 1 the tanh
                             // form of gelu (in float on the accumulators, the product rounded once)
-    int unary;              // act 0 with tokens on rows: an activation on every output, after the row's scale
+    int unary;              // act 0: an activation on every output (with tokens on rows: after the row's scale)
                             // (1 gelu by tanh, 2 silu, 3 gelu by erf; 0: none)
     // grouped product (tokens on rows): tile ta of A multiplies the rows [tile_expert[ta] * N, +N) of the B operand,
     // which stacks `experts` matrices of N rows; only the first *tiles_used tiles of A exist
@@ -167,8 +167,9 @@ __device__ __forceinline__ void gt_store16(const GemmParams& p, int row_a, int c
             for (int c = 0; c < 16; ++c) {
                 const int m = col0 + c;
                 if (m < p.M) {
-                    if (p.out_f32) ((float*)p.C)[(size_t)m * p.ldc + row_a] = v[c];
-                    else ((bf16*)p.C)[(size_t)m * p.ldc + row_a] = __float2bfloat16_rn(v[c]);
+                    const float x = p.unary ? unary_act(v[c], p.unary) : v[c];
+                    if (p.out_f32) ((float*)p.C)[(size_t)m * p.ldc + row_a] = x;
+                    else ((bf16*)p.C)[(size_t)m * p.ldc + row_a] = __float2bfloat16_rn(x);
                 }
             }
         }
@@ -223,10 +224,11 @@ __device__ __forceinline__ void gt_stage16(const GemmParams& p, unsigned char* s
         for (int c = 0; c < 8; ++c) reinterpret_cast<bf16*>(stage)[(col0 + first + c) * 64 + (f >> 1)] = o[c];
     } else if (p.out_f32) {
 #pragma unroll
-        for (int c = 0; c < 16; ++c) reinterpret_cast<float*>(stage)[(col0 + c) * 128 + f] = v[c];
+        for (int c = 0; c < 16; ++c) reinterpret_cast<float*>(stage)[(col0 + c) * 128 + f] = p.unary ? unary_act(v[c], p.unary) : v[c];
     } else {
 #pragma unroll
-        for (int c = 0; c < 16; ++c) reinterpret_cast<bf16*>(stage)[(col0 + c) * 128 + f] = __float2bfloat16_rn(v[c]);
+        for (int c = 0; c < 16; ++c)
+            reinterpret_cast<bf16*>(stage)[(col0 + c) * 128 + f] = __float2bfloat16_rn(p.unary ? unary_act(v[c], p.unary) : v[c]);
     }
 }
 // gt_flush: the staged tile (tokens tb*BN .., features ta*128 ..) to C, by the 128 epilogue threads

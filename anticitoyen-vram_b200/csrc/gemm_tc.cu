@@ -822,7 +822,7 @@ static int gemm_tc_run(GemmParams& p, const void* x, int ldx, const void* w, int
     p.gate_fn = p.act == 1 ? act >> 4 : 0;
     p.unary = p.act == 0 ? act >> 4 : 0;
     act = p.act;
-    if (p.gate_fn > 1 || p.unary > 3 || ((p.unary || (p.row_scale && act == 0)) && (swap || splits > 1))) return ACV_ERR_SIZE;
+    if (p.gate_fn > 1 || p.unary > 3 || (p.row_scale && act == 0 && (swap || splits > 1))) return ACV_ERR_SIZE;
     if (act && (out_f32 || (N & 1))) return ACV_ERR_SIZE;
     if (act == 2 && swap) return ACV_ERR_SIZE;
     if (p.tile_expert && (swap || splits > 1 || (flags & 6) || p.experts < 1 || (N % 8))) return ACV_ERR_SIZE;

@@ -462,7 +462,7 @@ def gemm_tc_plan(M: int, N: int, K: int, sms: int | None = None, bn_multiple: in
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | None = None,
             swiglu_pairs: bool = False, static_weights: bool = False, bias: torch.Tensor | None = None,
-            gate_fn: int = 0) -> torch.Tensor:
+            gate_fn: int = 0, unary: str | None = None) -> torch.Tensor:
     """out[M,N] = x[M,K] @ w[N,K]^T (+ bias) on tcgen05; x, w bfloat16, out bfloat16 or float32; ``bias`` float32 [N],
     added in the epilogue to the float accumulator (before the activation of the paired form).
 
@@ -471,8 +471,11 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | N
 
     With ``swiglu_pairs`` the rows of w come in (gate, up) pairs and out is [M, N/2]:
     out[:, i] = silu(x . w[2i]) * (x . w[2i+1]), rounded as the separate kernels round; with ``gate_fn`` 1 the gate
-    passes through the tanh form of gelu instead (in float on the accumulators, the product rounded once)."""
+    passes through the tanh form of gelu instead (in float on the accumulators, the product rounded once).
+    ``unary`` (not with ``swiglu_pairs``): an activation of ``ACTIVATIONS`` (not the first) on every output."""
     _need_cuda(x, w, out)
+    if unary is not None and (swiglu_pairs or ACTIVATIONS.get(unary, 0) == 0):
+        raise KernelError(f"gemm_tc: no activation '{unary}' in the epilogue (or asked for beside the paired form)")
     M, K = x.shape
     N = w.shape[0]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
@@ -489,7 +492,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | N
     tiles = (-(-N // 128) * -(-M // bn)) if swap else (-(-M // 128) * -(-N // bn))
     ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)
     args = (_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K,
-            1 if out.dtype == torch.float32 else 0, (1 | (int(gate_fn) << 4)) if swiglu_pairs else 0, swap, bn, splits, _p(ws),
+            1 if out.dtype == torch.float32 else 0,
+            (1 | (int(gate_fn) << 4)) if swiglu_pairs else ((ACTIVATIONS[unary] << 4) if unary else 0), swap, bn, splits, _p(ws),
             ws.numel(), _p(cnt),
             cnt.numel(), _p(status), sm_count(x.device), stages, cluster | (2 if static_weights else 0))
     if bias is not None:
@@ -981,14 +985,18 @@ def decode_layer(x: torch.Tensor, delta: torch.Tensor | None, delta_out: torch.T
 
 
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, static_weights: bool = False,
-                bias: torch.Tensor | None = None) -> torch.Tensor:
+                bias: torch.Tensor | None = None, unary: str | None = None) -> torch.Tensor:
     """out = x @ w^T (+ bias) in bfloat16 with float accumulation: the tcgen05 kernel, the bias in its epilogue; rows
     that are not 16-byte aligned (K or a stride no multiple of 8) go to the library product, as all do in the
-    reference, and a kernel of its own adds the bias."""
+    reference, and a kernel of its own adds the bias.  ``unary`` (a name of ``ACTIVATIONS`` other than the first): that
+    activation of every output, in the product's epilogue on the float accumulators (or by a kernel of its own behind
+    the library product)."""
     if gemm_tc_takes(x, w):
-        return gemm_tc(x, w, out, static_weights=static_weights, bias=bias)
+        return gemm_tc(x, w, out, static_weights=static_weights, bias=bias, unary=unary)
     torch.mm(x, w.t(), out=out)
-    return add_bias(out, bias) if bias is not None else out
+    if bias is not None:
+        add_bias(out, bias)
+    return activation(out, out, unary) if unary else out
 
 
 def linear_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor,

@@ -305,9 +305,7 @@ class RoutedExperts(FeedForward):
             ops.moe_experts_down(act, self.down, parts, grouped, tile_expert, w_out, top)
         shared = None
         if self.shared_ff and self.plain:
-            sact = self.shared_gate_up(h)
-            ops.activation(sact, sact, self.activation)
-            shared = self.shared_down(sact)
+            shared = self.shared_down(self.shared_gate_up(h, unary=self.activation))
         elif self.shared_ff:
             sact = torch.empty((T, self.shared_ff), device=dev, dtype=h.dtype)
             if self.shared_pairs and ops.linear_bf16_glu_takes(h, self.shared_gate_up.weight):

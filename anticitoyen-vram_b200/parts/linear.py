@@ -53,9 +53,11 @@ class Linear:
     def flops(self, tokens: int) -> float:
         return 2.0 * tokens * self.out_features * self.in_features
 
-    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, plan: tuple | None = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, plan: tuple | None = None,
+                 unary: str | None = None) -> torch.Tensor:
         """``plan``: how the tensor-core product tiles and splits this call (``ops.gemm_tc``), for a caller that knows
-        its shape better than the general rules do."""
+        its shape better than the general rules do.  ``unary``: an activation (a name of ``ops.ACTIVATIONS``) on every
+        output: in the tensor-core product's epilogue where that product runs, by a kernel of its own otherwise."""
         w = self.weight
         out_dtype = out_dtype or x.dtype
         out = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=out_dtype)
@@ -70,5 +72,8 @@ class Linear:
         elif out_dtype == torch.float32:
             ops.linear_bf16_f32out(x, w, out, static_weights=True, bias=self.bias)
         else:
-            ops.linear_bf16(x, w, out, static_weights=True, bias=self.bias)      # (the tensor-core product adds it itself)
+            # (the tensor-core product adds the bias, and applies the activation, itself)
+            return ops.linear_bf16(x, w, out, static_weights=True, bias=self.bias, unary=unary)
+        if unary is not None:
+            ops.activation(out, out, unary)
         return out
