@@ -315,7 +315,10 @@ class TimeMix(SegmentedRecurrence):
         r, k, v = (self.proj[role](x[i], out_dtype=torch.float32) for i, role in enumerate(("r", "k", "v")))
         gate = self.proj["g"](x[3])
         decay = torch.empty((T, I), device=h.device, dtype=torch.float32)
-        ops.wkv_decay(self.w1(x[4], out_dtype=torch.float32), self.w2_t, self.w0, decay)
+        # many tokens against a few dozen rows of W1: one column of tiles, so the reduction is split eight ways to put
+        # more than a ninth of the SMs to work
+        plan = (0, 128, 8, 4, 0) if h.dtype == torch.bfloat16 and T >= 512 and self.hidden_size >= 2048 and self.rank <= 128 else None
+        ops.wkv_decay(self.w1(x[4], out_dtype=torch.float32, plan=plan), self.w2_t, self.w0, decay)
         o = torch.empty((T, I), device=h.device, dtype=torch.float32)
         ops.wkv(r, k, v, decay, self.u, state.state, ctx.state_slots[state.group], ctx.cu_q, ctx.num_seqs, o, H, D, D,
                 work=ctx.work.get(self.metadata_key))
