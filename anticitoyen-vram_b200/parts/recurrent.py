@@ -317,7 +317,8 @@ class TimeMix(SegmentedRecurrence):
         decay = torch.empty((T, I), device=h.device, dtype=torch.float32)
         # many tokens against a few dozen rows of W1: one column of tiles, so the reduction is split eight ways to put
         # more than a ninth of the SMs to work
-        plan = (0, 128, 8, 4, 0) if h.dtype == torch.bfloat16 and T >= 512 and self.hidden_size >= 2048 and self.rank <= 128 else None
+        plan = (0, 128, 8, 4, 0) if h.dtype == torch.bfloat16 and T >= 512 and self.hidden_size >= 2048 \
+            and self.rank <= 128 and self.rank % 8 == 0 else None
         ops.wkv_decay(self.w1(x[4], out_dtype=torch.float32, plan=plan), self.w2_t, self.w0, decay)
         o = torch.empty((T, I), device=h.device, dtype=torch.float32)
         ops.wkv(r, k, v, decay, self.u, state.state, ctx.state_slots[state.group], ctx.cu_q, ctx.num_seqs, o, H, D, D,
